@@ -24,6 +24,16 @@ def group_layers(needs: List[CacheNeed]) -> Tuple[List[Tuple[int, int, int, int,
     keys: List[Tuple[int, int, int, int, bool]] = []
     of_layer: List[int] = []
     for need in needs:
+        if need.kind == "multi":
+            # the page-holding parts of a mixer made of mixers join the groups like layers of their own;
+            # the need itself holds no pages
+            for part in need.flat():
+                if part.kind == "kv":
+                    key = (part.kv_heads, part.head_dim, part.window, part.value_dim, part.values_in_keys)
+                    if key not in keys:
+                        keys.append(key)
+            of_layer.append(-1)
+            continue
         if need.kind != "kv":
             of_layer.append(-1)
             continue
@@ -36,9 +46,11 @@ def group_layers(needs: List[CacheNeed]) -> Tuple[List[Tuple[int, int, int, int,
 
 def bytes_per_page(needs: List[CacheNeed], page_size: int, elem_size: int) -> List[int]:
     """Per group, the bytes one page number costs across the group's layers."""
-    keys, of_layer = group_layers(needs)
+    keys, _ = group_layers(needs)
+    flat = [f for need in needs for f in need.flat()]
+    _, of_layer = group_layers(flat)
     out = [0] * len(keys)
-    for need, g in zip(needs, of_layer):
+    for need, g in zip(flat, of_layer):
         if g >= 0:
             width = need.head_dim + (0 if need.values_in_keys else need.value_dim)
             out[g] += need.kv_heads * page_size * width * elem_size
@@ -56,26 +68,29 @@ class CachePools:
         self.table = PageTable(self.groups, max_requests) if keys else PageTable(
             [GroupSpec(0, page_size, 0)], max_requests)
         self.page_size = page_size
-        self.layers: List[LayerCache] = []
-        for need, g in zip(needs, self.group_of_layer):
+        def storage(need: CacheNeed) -> LayerCache:
+            if need.kind == "multi":
+                return LayerCache(need, -1, parts=tuple(storage(p) for p in need.parts))
             if need.kind == "kv":
+                g = keys.index((need.kv_heads, need.head_dim, need.window, need.value_dim, need.values_in_keys))
                 k_shape = (pages_per_group[g], need.kv_heads, page_size, need.head_dim)
                 v_shape = (pages_per_group[g], need.kv_heads, page_size, need.value_dim)
                 # zeros, not uninitialised memory: rows that a tile loads but masks must be finite
                 k_pool = torch.zeros(k_shape, dtype=dtype, device=device)
                 v_pool = k_pool if need.values_in_keys else torch.zeros(v_shape, dtype=dtype, device=device)
-                self.layers.append(LayerCache(need, g, k_pool, v_pool, page_size))
-            elif need.kind == "state":
+                return LayerCache(need, g, k_pool, v_pool, page_size)
+            if need.kind == "state":
                 st = torch.zeros((max_requests, *need.state_shape), dtype=need.state_dtype,
                                  device=device)
-                self.layers.append(LayerCache(need, -1, state=st))
-            else:
-                self.layers.append(LayerCache(need))
+                return LayerCache(need, -1, state=st)
+            return LayerCache(need)
+
+        self.layers: List[LayerCache] = [storage(need) for need in needs]
 
     def nbytes(self) -> int:
-        n = 0
-        for lc in self.layers:
-            for t in (lc.k, lc.v if lc.v is not lc.k else None, lc.state):
-                if t is not None:
-                    n += t.numel() * t.element_size()
-        return n
+        def size(lc: LayerCache) -> int:
+            own = sum(t.numel() * t.element_size() for t in (lc.k, lc.v if lc.v is not lc.k else None, lc.state)
+                      if t is not None)
+            return own + sum(size(p) for p in lc.parts)
+
+        return sum(size(lc) for lc in self.layers)

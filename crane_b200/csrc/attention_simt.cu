@@ -26,14 +26,20 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
                             const int* __restrict__ positions, const int* __restrict__ tok_entry,
                             const int* __restrict__ block_table, int max_blocks, int num_pages,
                             int page_size, int n_tokens, int nq, int nkv, int d, int dv,
-                            int v_stride, int window, float scale, int sink, int* err) {
+                            int v_stride, int window, float scale, int sink, float* __restrict__ out_cross,
+                            int* err) {
     extern __shared__ float q_all[];              // [WARPS][d]
     float* q_s = q_all + (threadIdx.x >> 5) * d;
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * WARPS + wib;
-    if (warp >= (long long)n_tokens * nq) return;
-    const int t = (int)(warp / nq), h = (int)(warp % nq);
+    // `out_cross`: every query head is paired with every key/value head's values (its keys stay its own
+    // group's): nq * nkv warps a token, results float [token][query head][value head][dv]
+    const int pairs = out_cross != nullptr ? nq * nkv : nq;
+    if (warp >= (long long)n_tokens * pairs) return;
+    const int t = (int)(warp / pairs), hv = (int)(warp % pairs);
+    const int h = out_cross != nullptr ? hv / nkv : hv;
     const int g = h / (nq / nkv);
+    const int gv = out_cross != nullptr ? hv % nkv : g;
     const int pos = positions[t];
     if (tok_entry[t] < 0) return;                 // a row that pads the step: it attends to nothing
     const int* table = block_table + (long long)tok_entry[t] * max_blocks;
@@ -48,6 +54,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
     bool bad = false;
+    const long long v_shift = (long long)(gv - g) * page_size;      // from a key row to the value row read with it
 
     for (int base = lo; base <= pos; base += 32) {
         const int j = base + lane;
@@ -78,7 +85,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long rj = __shfl_sync(0xffffffffu, row, jj);
             if (rj < 0) continue;
-            const T* vp = v_pool + rj * v_stride;
+            const T* vp = v_pool + (rj + v_shift) * v_stride;
 #pragma unroll
             for (int i = 0; i < NACC; ++i) {
                 const int c = lane + 32 * i;
@@ -90,6 +97,15 @@ paged_attention_simt_kernel(const T* __restrict__ q, T* __restrict__ out,
     // a sink: one more candidate of score 0 that has no value, so it only adds exp(0 - m) to the sum
     if (sink) l += expf(-m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (out_cross != nullptr) {
+        float* op = out_cross + ((long long)t * pairs + hv) * dv;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dv) op[c] = acc[i] * inv;
+        }
+        return;
+    }
     T* op = out + ((long long)t * nq + h) * dv;
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
@@ -104,23 +120,23 @@ CRANE_API int crane_paged_attention_simt(int dtype, const void* q, void* out, co
                                          const int* tok_entry, const int* block_table,
                                          int max_blocks, int num_pages, int page_size,
                                          int n_tokens, int nq, int nkv, int d, int dv,
-                                         int v_stride, int window, float scale, int sink, int* err,
-                                         cudaStream_t st) {
+                                         int v_stride, int window, float scale, int sink, float* out_cross,
+                                         int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (d > MAXD || d <= 0 || dv > MAXDV || dv <= 0 || v_stride < dv || nkv <= 0 || nq % nkv != 0)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)WARPS * d * sizeof(float);
-    const long long warps = (long long)n_tokens * nq;
+    const long long warps = (long long)n_tokens * nq * (out_cross != nullptr ? nkv : 1);
     const int blocks = (int)((warps + WARPS - 1) / WARPS);
     if (dtype == 0)
         paged_attention_simt_kernel<float><<<blocks, WARPS * 32, smem, st>>>(
             (const float*)q, (float*)out, (const float*)k_pool, (const float*)v_pool, positions,
             tok_entry, block_table, max_blocks, num_pages, page_size, n_tokens, nq, nkv, d, dv,
-            v_stride, window, scale, sink, err);
+            v_stride, window, scale, sink, out_cross, err);
     else
         paged_attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, smem, st>>>(
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, tok_entry, block_table, max_blocks, num_pages,
-            page_size, n_tokens, nq, nkv, d, dv, v_stride, window, scale, sink, err);
+            page_size, n_tokens, nq, nkv, d, dv, v_stride, window, scale, sink, out_cross, err);
     return crane_launch_status();
 }

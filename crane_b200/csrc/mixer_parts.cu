@@ -27,13 +27,25 @@ projection_norm_cache_kernel(GemmOut<T> qkv, int cols, const int* __restrict__ p
                              int max_blocks, int num_pages, int page_size, const float* __restrict__ qw,
                              const float* __restrict__ kw, float eps, T* __restrict__ q_out,
                              T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int dv,
-                             int d_store, int dv_store, int* err) {
+                             int d_store, int dv_store, const float* __restrict__ cos_tab,
+                             const float* __restrict__ sin_tab, int n_positions, int rot_dims,
+                             const float* __restrict__ q_head_scale, int* err) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int e = tok_entry[t];
     if (e < 0) return;
+    // Rotary positions (after the norms): the leading rot_dims elements of every query and key head,
+    // element i paired with i + rot_dims / 2, by the angles of the token's row of the tables.
+    const int half = cos_tab != nullptr ? rot_dims >> 1 : 0;
+    const int rpos = positions[t];
+    if (half > 0 && (rpos < 0 || rpos >= n_positions)) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_POSITION_RANGE);
+        return;
+    }
+    const float* ct = cos_tab + (long long)rpos * half;
+    const float* sn = sin_tab + (long long)rpos * half;
     const long long base = (long long)t * cols;
     const int nqd = nq * d, nkd = nkv * d, nvd = nkv * dv;
     float sq = 0.f, sk = 0.f;
@@ -51,6 +63,12 @@ projection_norm_cache_kernel(GemmOut<T> qkv, int cols, const int* __restrict__ p
         const int h = c / d_store, i = c % d_store;
         float v = 0.f;
         if (i < d) v = qkv.load(base + h * d + i) * rq * (qw != nullptr ? qw[h * d + i] : 1.f);
+        if (i < 2 * half) {
+            const int j = i < half ? i + half : i - half, a = i < half ? i : i - half;
+            const float o = qkv.load(base + h * d + j) * rq * (qw != nullptr ? qw[h * d + j] : 1.f);
+            v = i < half ? v * ct[a] - o * sn[a] : v * ct[a] + o * sn[a];
+        }
+        if (q_head_scale != nullptr) v *= q_head_scale[h];
         q_out[(long long)t * nq * d_store + c] = from_f32<T>(v);
     }
     const int pos = positions[t];
@@ -66,6 +84,11 @@ projection_norm_cache_kernel(GemmOut<T> qkv, int cols, const int* __restrict__ p
         const int g = c / d_store, i = c % d_store;
         float v = 0.f;
         if (i < d) v = qkv.load(base + nqd + g * d + i) * rk * (kw != nullptr ? kw[g * d + i] : 1.f);
+        if (i < 2 * half) {
+            const int j = i < half ? i + half : i - half, a = i < half ? i : i - half;
+            const float o = qkv.load(base + nqd + g * d + j) * rk * (kw != nullptr ? kw[g * d + j] : 1.f);
+            v = i < half ? v * ct[a] - o * sn[a] : v * ct[a] + o * sn[a];
+        }
         k_pool[(((long long)page * nkv + g) * page_size + slot) * d_store + i] = from_f32<T>(v);
     }
 #pragma unroll 4
@@ -549,15 +572,19 @@ CRANE_API int crane_projection_norm_cache(int dtype, const void* qkv, const floa
                                           const int* tok_entry, const int* block_table, int max_blocks,
                                           int num_pages, int page_size, const float* qw, const float* kw,
                                           float eps, void* q_out, void* k_pool, void* v_pool, int n_tokens,
-                                          int nq, int nkv, int d, int dv, int d_store, int dv_store, int* err,
-                                          cudaStream_t st) {
+                                          int nq, int nkv, int d, int dv, int d_store, int dv_store,
+                                          const float* cos_tab, const float* sin_tab, int n_positions,
+                                          int rot_dims, const float* q_head_scale, int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (d_store < d || dv_store < dv) return (int)cudaErrorInvalidValue;
+    if (cos_tab != nullptr && (rot_dims < 0 || rot_dims > d || rot_dims % 2 || sin_tab == nullptr))
+        return (int)cudaErrorInvalidValue;
     DISPATCH_T(dtype, {
         GemmOut<T> g{(const T*)qkv, qkv_parts, n_parts, part_stride};
         return crane_launch(projection_norm_cache_kernel<T>, dim3(n_tokens), dim3(256), 0, st, g, cols, positions,
                             tok_entry, block_table, max_blocks, num_pages, page_size, qw, kw, eps, (T*)q_out,
-                            (T*)k_pool, (T*)v_pool, nq, nkv, d, dv, d_store, dv_store, err);
+                            (T*)k_pool, (T*)v_pool, nq, nkv, d, dv, d_store, dv_store, cos_tab, sin_tab,
+                            n_positions, rot_dims, q_head_scale, err);
     });
 }
 

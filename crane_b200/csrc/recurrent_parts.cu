@@ -1,0 +1,425 @@
+// Linear recurrences with one matrix state S [dk, dv] per head and request, and what surrounds them.
+//
+//     S <- diag(w_t) S                       (w_t: a decay per key channel, or one number per head)
+//     u  = beta_t (v_t - S^T k_t)            (`delta`: the delta rule's correction; else u = v_t)
+//     S <- S + k_t u^T
+//     o_t = S^T q_t                          (the read-out sees the token's own write)
+//
+// `matrix_state_scan` walks each request's tokens in order.  Columns of S do not talk to one another:
+// a CTA holds a block of columns of one (request, head), a column's rows spread over LANES lanes of a
+// warp (ROWS rows each, in registers), dot products over the rows finished by shuffles.  The inputs of
+// every token (q, k, v, w, beta) are 32-bit rows of an `aux` buffer that a prep kernel writes:
+//   * `conv_delta_prep`: q, k, v through a short causal convolution over time and silu, q and k scaled
+//     to unit length per head, beta = sigmoid(.), w = exp(-exp(A) softplus(. + dt)) per head; the last
+//     taps - 1 inputs of the convolutions are part of the request's state (`conv_state_update`);
+//   * `decay_gate_prep`: q scaled, k, v, and w = sigmoid(z)^(1 / tau) per key channel with z a
+//     low-rank product plus bias.
+// `head_norm_gate` norms each head's read-out over dv, applies the weight and silu(gate).
+// `head_talk_mix` and `pair_norm_mean` belong to attention whose heads exchange their weights and to
+// two mixers side by side.
+// The state lives in 32-bit in the request's slot, in the order the scan's threads hold it:
+// [head][row / LANES][column][row % LANES]; a request whose first token is in the step starts from zero.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// ------------------------------------------------------ convolution + delta-rule inputs
+// proj row: [q (G d) | k (G d) | v (H dv) | gate (H dv) | b (H) | a (H)].  aux row: [q (G d) | k (G d) |
+// v (H dv) | w (H) | beta (H)].  conv_w [2 G d + H dv][taps] float.  conv_state: inside the slot's state
+// at `conv_off`, [taps - 1][C].  One CTA per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_delta_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_entry,
+                       const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                       const int* __restrict__ slots, int n_slots, const float* __restrict__ state,
+                       long long slot_stride, long long conv_off, const float* __restrict__ conv_w, int taps,
+                       const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                       float* __restrict__ aux, int aux_cols, int H, int G, int d, int dv, float key_eps,
+                       float q_scale, int* err) {
+    extern __shared__ float vals[];                   // [C]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int e = tok_entry[t];
+    if (e < 0) return;
+    const int C = 2 * G * d + H * dv;
+    const int first = cu_q[e];
+    const int i = t - first;                                         // the token's place in its portion
+    const int start = kv_len[e] - (cu_q[e + 1] - first);             // tokens of the request before the step
+    const int slot = slots[e];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
+        return;
+    }
+    const float* cs = state + (long long)slot * slot_stride + conv_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;
+            float x = 0.f;
+            if (i - back >= 0) x = proj.load((long long)(t - back) * cols + c);
+            else if (start + i - back >= 0) x = cs[(long long)(taps - 1 + i - back) * C + c];
+            acc = fmaf(conv_w[(long long)c * taps + j], x, acc);
+        }
+        vals[c] = silu_f(acc);
+    }
+    __syncthreads();
+    float* out = aux + (long long)t * aux_cols;
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int hd = wib; hd < 2 * G; hd += nw) {                        // q heads, then k heads
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) { const float v = vals[hd * d + c]; ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        const float r = rsqrtf(ss + key_eps) * (hd < G ? q_scale : 1.f);
+        for (int c = lane; c < d; c += 32) out[hd * d + c] = vals[hd * d + c] * r;
+    }
+    for (int c = threadIdx.x; c < H * dv; c += blockDim.x) out[2 * G * d + c] = vals[2 * G * d + c];
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const long long row = (long long)t * cols + C + H * dv;
+        const float b = proj.load(row + h), a = proj.load(row + H + h);
+        out[C + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+        out[C + H + h] = 1.f / (1.f + expf(-b));
+    }
+}
+
+// One thread per (entry, channel): the last taps - 1 inputs of the channel after this step.
+constexpr int MAX_TAPS = 16;
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_state_update_kernel(GemmOut<T> proj, int cols, const int* __restrict__ cu_q,
+                         const int* __restrict__ kv_len, const int* __restrict__ slots, int n_slots,
+                         float* __restrict__ state, long long slot_stride, long long conv_off, int taps, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int first = cu_q[e], q_len = cu_q[e + 1] - first;
+    if (q_len <= 0 || c >= C) return;
+    const int slot = slots[e];
+    if (slot < 0 || slot >= n_slots) return;
+    const int end = kv_len[e], start = end - q_len;
+    float* cs = state + (long long)slot * slot_stride + conv_off;
+    float old[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) old[j] = (j < taps - 1) ? cs[(long long)j * C + c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+        if (j < taps - 1) {
+            const int p = end - (taps - 1) + j;
+            float v = 0.f;
+            if (p >= start) v = proj.load((long long)(first + p - start) * cols + c);
+            else if (p >= 0) {
+                const int k = taps - 1 + p - start;
+                float o = 0.f;
+#pragma unroll
+                for (int m = 0; m < MAX_TAPS; ++m) if (m == k) o = old[m];
+                v = o;
+            }
+            cs[(long long)j * C + c] = v;
+        }
+    }
+}
+
+// ------------------------------------------------------ inputs of the recurrence with a decay per channel
+// proj row: [q (H d) | k (H d) | v (H dv) | gate (H dv) | low (rank)].  aux row: [q (H d) | k (H d) |
+// v (H dv) | w (H d)].  a2t [rank][H d] float, bias [H d].
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_gate_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_entry,
+                       const float* __restrict__ a2t, const float* __restrict__ bias, int rank,
+                       float inv_tau, float q_scale, float* __restrict__ aux, int aux_cols, int H, int d, int dv) {
+    extern __shared__ float low[];                    // [rank]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (tok_entry[t] < 0) return;
+    const int hd = H * d, hv = H * dv;
+    const long long row = (long long)t * cols;
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) low[r] = proj.load(row + 2 * hd + 2 * hv + r);
+    __syncthreads();
+    float* out = aux + (long long)t * aux_cols;
+    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
+        out[c] = proj.load(row + c) * q_scale;
+        out[hd + c] = proj.load(row + hd + c);
+        float z = bias[c];
+        for (int r = 0; r < rank; ++r) z = fmaf(low[r], a2t[(long long)r * hd + c], z);
+        // sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau)
+        out[2 * hd + hv + c] = expf(-softplus_f(-z) * inv_tau);
+    }
+    for (int c = threadIdx.x; c < hv; c += blockDim.x) out[2 * hd + c] = proj.load(row + 2 * hd + c);
+}
+
+// ------------------------------------------------------ the recurrence
+// grid (entries, heads, column blocks); block = COLS columns x LANES lanes.  aux offsets: q_off, k_off,
+// v_off, w_off, beta_off (beta only with `delta`); q/k head of head h is h / qk_rep; w is [Hqk d]
+// (w_vec) or [H].  o_raw float [n][H dv].
+constexpr int SCAN_TOKENS = 8;
+template <int ROWS>
+__global__ void __launch_bounds__(256)
+matrix_state_scan_kernel(const float* __restrict__ aux, int aux_cols, int q_off, int k_off, int v_off, int w_off,
+                         int beta_off, int w_vec, int delta, int qk_rep, const int* __restrict__ cu_q,
+                         const int* __restrict__ kv_len, const int* __restrict__ slots, int n_slots,
+                         float* __restrict__ state, long long slot_stride, float* __restrict__ o_raw,
+                         int H, int dk, int dv, int lanes, int cols_per_block, int* err) {
+    extern __shared__ float tile[];                   // [SCAN_TOKENS][3 dk + cols + 2]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.x, h = blockIdx.y;
+    const int first = cu_q[e], q_len = cu_q[e + 1] - first;
+    if (q_len <= 0) return;
+    const int slot = slots[e];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
+        return;
+    }
+    const int start = kv_len[e] - q_len;
+    const int lane = threadIdx.x % lanes, cl = threadIdx.x / lanes;
+    const int col = blockIdx.z * cols_per_block + cl;
+    const bool live = cl < cols_per_block && col < dv;
+    // state [H][ROWS][dv][lanes]
+    float* sp = state + (long long)slot * slot_stride + (long long)h * ROWS * dv * lanes;
+    float s[ROWS];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+        s[i] = (live && start > 0) ? sp[((long long)i * dv + col) * lanes + lane] : 0.f;
+    const int hq = h / qk_rep;
+    const int stride = 3 * dk + cols_per_block + 2;
+    const int c0 = blockIdx.z * cols_per_block;
+    for (int t0 = 0; t0 < q_len; t0 += SCAN_TOKENS) {
+        const int nt = min(SCAN_TOKENS, q_len - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * stride; idx += blockDim.x) {
+            const int tt = idx / stride, j = idx % stride;
+            const float* a = aux + (long long)(first + t0 + tt) * aux_cols;
+            float v;
+            if (j < dk) v = a[q_off + hq * dk + j];
+            else if (j < 2 * dk) v = a[k_off + hq * dk + j - dk];
+            else if (j < 3 * dk) v = w_vec ? a[w_off + hq * dk + j - 2 * dk] : 0.f;
+            else if (j < 3 * dk + cols_per_block) {
+                const int c = c0 + j - 3 * dk;
+                v = c < dv ? a[v_off + h * dv + c] : 0.f;
+            } else if (j == 3 * dk + cols_per_block) v = w_vec ? 1.f : a[w_off + h];
+            else v = delta ? a[beta_off + h] : 1.f;
+            tile[idx] = v;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* q = tile + tt * stride;
+            const float* k = q + dk;
+            const float* w = k + dk;
+            const float vv = cl < cols_per_block ? q[3 * dk + cl] : 0.f;
+            const float ws = q[3 * dk + cols_per_block], beta = q[3 * dk + cols_per_block + 1];
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+                const int r = lane + i * lanes;
+                if (r < dk) {
+                    s[i] *= w_vec ? w[r] : ws;
+                    dot = fmaf(s[i], k[r], dot);
+                }
+            }
+            float u = vv;
+            if (delta) {
+                for (int o = lanes >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                u = beta * (vv - dot);
+            }
+            float rd = 0.f;
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+                const int r = lane + i * lanes;
+                if (r < dk) {
+                    s[i] = fmaf(k[r], u, s[i]);
+                    rd = fmaf(s[i], q[r], rd);
+                }
+            }
+            for (int o = lanes >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
+            if (live && lane == 0) o_raw[(long long)(first + t0 + tt) * H * dv + h * dv + col] = rd;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) sp[((long long)i * dv + col) * lanes + lane] = s[i];
+    }
+}
+
+// ------------------------------------------------------ head norm and gate
+// out[t][h dv + c] = o_raw / rms_over_dv(o_raw) * norm_w[c] * silu(gate[t][gate_off + h dv + c]); a warp per
+// (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ o_raw, GemmOut<T> proj, int cols, int gate_off,
+                      const int* __restrict__ tok_entry, const float* __restrict__ norm_w, float eps,
+                      T* __restrict__ out, int n, int H, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)n * H) return;
+    const int t = (int)(wid / H), h = (int)(wid % H);
+    if (tok_entry[t] < 0) return;
+    const float* o = o_raw + ((long long)t * H + h) * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) { const float v = o[c]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)dv + eps);
+    for (int c = lane; c < dv; c += 32) {
+        const float g = proj.load((long long)t * cols + gate_off + h * dv + c);
+        out[((long long)t * H + h) * dv + c] = from_f32<T>(o[c] * rstd * norm_w[c] * silu_f(g));
+    }
+}
+
+// ------------------------------------------------------ heads that exchange their weights
+// cross [n][H][G][dv] float: query head g's softmax weights applied to the values of every key/value
+// head.  out[t][h] = sum_g talk[h][g] cross[t][g][h / (H / G)].
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_talk_mix_kernel(const float* __restrict__ cross, const float* __restrict__ talk,
+                     const int* __restrict__ tok_entry, T* __restrict__ out, int H, int G, int dv, int out_head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (tok_entry[t] < 0) return;
+    const int rep = H / G;
+    for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
+        const int h = idx / dv, c = idx % dv;
+        const float* src = cross + ((long long)t * H * G + h / rep) * dv + c;
+        float acc = 0.f;
+        for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], src[(long long)g * G * dv], acc);
+        out[((long long)t * H + h) * out_head + c] = from_f32<T>(acc);
+    }
+}
+
+// ------------------------------------------------------ two mixers side by side
+// out = (a / rms(a) * wa + b / rms(b) * wb) / 2 over the width; a CTA per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pair_norm_mean_kernel(GemmOut<T> a, GemmOut<T> b, const float* __restrict__ wa, const float* __restrict__ wb,
+                      float eps, T* __restrict__ out, int hidden) {
+    extern __shared__ float row2[];                   // [2 hidden]
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long base = (long long)blockIdx.x * hidden;
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float x = a.load(base + c), y = b.load(base + c);
+        row2[c] = x;
+        row2[hidden + c] = y;
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ra = rsqrtf(sa / (float)hidden + eps), rb = rsqrtf(sb / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        out[base + c] = from_f32<T>(0.5f * (row2[c] * ra * wa[c] + row2[hidden + c] * rb * wb[c]));
+}
+
+}  // namespace
+
+CRANE_API int crane_conv_delta_prep(int dtype, const void* proj, const float* proj_parts, int n_parts,
+                                    long long part_stride, int cols, const int* tok_entry, const int* cu_q,
+                                    const int* kv_len, const int* slots, int n_slots, float* state,
+                                    long long slot_stride, long long conv_off, const float* conv_w, int taps,
+                                    const float* a_log, const float* dt_bias, float* aux, int aux_cols,
+                                    int n_tokens, int n_entries, int H, int G, int d, int dv, float key_eps,
+                                    float q_scale, int* err, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const int C = 2 * G * d + H * dv;
+    if (taps < 1 || taps > MAX_TAPS || (size_t)C * 4 > 160 * 1024) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)C * sizeof(float);
+    DISPATCH_T(dtype, {
+        GemmOut<T> p{(const T*)proj, proj_parts, n_parts, part_stride};
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(conv_delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int rc = crane_launch(conv_delta_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, st, p, cols, tok_entry,
+                              cu_q, kv_len, slots, n_slots, (const float*)state, slot_stride, conv_off, conv_w,
+                              taps, a_log, dt_bias, aux, aux_cols, H, G, d, dv, key_eps, q_scale, err);
+        if (rc != 0 || taps == 1) return rc;
+        return crane_launch(conv_state_update_kernel<T>, dim3((C + 127) / 128, n_entries), dim3(128), 0, st, p,
+                            cols, cu_q, kv_len, slots, n_slots, state, slot_stride, conv_off, taps, C);
+    });
+}
+
+CRANE_API int crane_decay_gate_prep(int dtype, const void* proj, const float* proj_parts, int n_parts,
+                                    long long part_stride, int cols, const int* tok_entry, const float* a2t,
+                                    const float* bias, int rank, float inv_tau, float q_scale, float* aux,
+                                    int aux_cols, int n_tokens, int H, int d, int dv, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (rank < 0 || rank > 8192) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, {
+        GemmOut<T> p{(const T*)proj, proj_parts, n_parts, part_stride};
+        return crane_launch(decay_gate_prep_kernel<T>, dim3(n_tokens), dim3(256), (size_t)(rank > 0 ? rank : 1) * 4,
+                            st, p, cols, tok_entry, a2t, bias, rank, inv_tau, q_scale, aux, aux_cols, H, d, dv);
+    });
+}
+
+// The scan's geometry for a key size: (rows per lane, lanes per column); 0 rows: too wide.
+CRANE_API int crane_matrix_state_plan(int dk, int* rows, int* lanes) {
+    int r = dk <= 256 ? 8 : 16, l = 1;
+    while (l * r < dk && l < 32) l *= 2;
+    if (l * r < dk) { *rows = 0; *lanes = 0; return 1; }
+    *rows = r;
+    *lanes = l;
+    return 0;
+}
+
+CRANE_API int crane_matrix_state_scan(const float* aux, int aux_cols, int q_off, int k_off, int v_off, int w_off,
+                                      int beta_off, int w_vec, int delta, int qk_rep, const int* cu_q,
+                                      const int* kv_len, const int* slots, int n_slots, float* state,
+                                      long long slot_stride, float* o_raw, int n_entries, int H, int dk, int dv,
+                                      int* err, cudaStream_t st) {
+    if (n_entries <= 0) return 0;
+    int rows, lanes;
+    if (crane_matrix_state_plan(dk, &rows, &lanes) || dv <= 0 || qk_rep <= 0) return (int)cudaErrorInvalidValue;
+    int cpb = 256 / lanes;
+    if (cpb > dv) cpb = dv;
+    const int blocks = (dv + cpb - 1) / cpb;
+    const int threads = ((cpb * lanes + 31) / 32) * 32;
+    const size_t smem = (size_t)SCAN_TOKENS * (3 * dk + cpb + 2) * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    auto kern = rows == 8 ? matrix_state_scan_kernel<8> : matrix_state_scan_kernel<16>;
+    return crane_launch(kern, dim3(n_entries, H, blocks), dim3(threads), smem, st, aux, aux_cols, q_off, k_off, v_off,
+                        w_off, beta_off, w_vec, delta, qk_rep, cu_q, kv_len, slots, n_slots, state, slot_stride,
+                        o_raw, H, dk, dv, lanes, cpb, err);
+}
+
+CRANE_API int crane_head_norm_gate(int dtype, const float* o_raw, const void* proj, const float* proj_parts,
+                                   int n_parts, long long part_stride, int cols, int gate_off,
+                                   const int* tok_entry, const float* norm_w, float eps, void* out, int n_tokens,
+                                   int H, int dv, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const long long warps = (long long)n_tokens * H;
+    DISPATCH_T(dtype, {
+        GemmOut<T> p{(const T*)proj, proj_parts, n_parts, part_stride};
+        return crane_launch(head_norm_gate_kernel<T>, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, st, o_raw, p,
+                            cols, gate_off, tok_entry, norm_w, eps, (T*)out, n_tokens, H, dv);
+    });
+}
+
+CRANE_API int crane_head_talk_mix(int dtype, const float* cross, const float* talk, const int* tok_entry, void* out,
+                                  int n_tokens, int H, int G, int dv, int out_head, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (G <= 0 || H % G) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, return crane_launch(head_talk_mix_kernel<T>, dim3(n_tokens), dim3(256), 0, st, cross, talk,
+                                          tok_entry, (T*)out, H, G, dv, out_head));
+}
+
+CRANE_API int crane_pair_norm_mean(int dtype, const void* a, const float* a_parts, int an, long long astr,
+                                   const void* b, const float* b_parts, int bn, long long bstr, const float* wa,
+                                   const float* wb, float eps, void* out, int n_rows, int hidden, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)2 * hidden * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    DISPATCH_T(dtype, {
+        GemmOut<T> ga{(const T*)a, a_parts, an, astr};
+        GemmOut<T> gb{(const T*)b, b_parts, bn, bstr};
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(pair_norm_mean_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return crane_launch(pair_norm_mean_kernel<T>, dim3(n_rows), dim3(256), smem, st, ga, gb, wa, wb, eps, (T*)out,
+                            hidden);
+    });
+}

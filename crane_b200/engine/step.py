@@ -158,7 +158,7 @@ class ModelRunner:
         self._graphs: Dict[object, tuple] = {}
         self._shape_seen: Dict[tuple, int] = {}      # how often a shape of small step has come
         self._graph_generation = -1
-        has_state = any(n.kind == "state" for n in self.model.cache_needs())
+        has_state = any(f.kind == "state" for n in self.model.cache_needs() for f in n.flat())
         self._graphs_ok = (self.cfg.use_cuda_graphs and not self.rt.exact and self.model.capturable()
                            and (not has_state or self.model.state_graph_safe()))
         # Steps of single tokens are padded to a batch-size bucket (rows of no entry, entries without
@@ -166,7 +166,8 @@ class ModelRunner:
         # steps with prompt portions are, to a shape of their own.
         # (State that only the embedding keeps, one token per request that its kernel reads and replaces
         # for entries with rows alone, bears the bucket's padding as well.)
-        mixer_state = any(n.kind == "state" for n in self.model.cache_needs()[:len(self.spec.schedule)])
+        mixer_state = any(f.kind == "state" for n in self.model.cache_needs()[:len(self.spec.schedule)]
+                          for f in n.flat())
         self._pad_with_copies = not mixer_state
         self.graph_replays = 0
         self.graph_captures = 0                    # steps that ran kernel by kernel and were recorded for their shape

@@ -28,7 +28,7 @@ _SIGNATURES = {
     "crane_gemm_simt": [I, I, P, P, P, P, I, I, I, L, L, L, P],
     "crane_gemm_bf16_tcgen05": [P, P, P, P, I, I, I, L, L, L, I, I, I, I, I, L, I, P, L, P, P],
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
-    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+    "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
     "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
     "crane_paged_prefill_attention_supports": [I, I, I],
@@ -50,7 +50,18 @@ _SIGNATURES = {
     "crane_token_gate": [I, P, P, I, L, P, P, I, I, I, P, I, I, P, I, P, P],
     "crane_ffn_activation": [I, P, P, I, L, P, I, I, I, P, I, I, I, P],
     "crane_route_topk": [P, P, P, P, I, I, I, P],
-    "crane_projection_norm_cache": [I, P, P, I, L, I, P, P, P, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, P, P],
+    "crane_projection_norm_cache": [I, P, P, I, L, I, P, P, P, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I,
+                                    P, P, I, I, P, P, P],
+    "crane_streams_norm": [I, P, L, I, P, P, P, I, L, P, P, P, P, P, P, I, I, F, P],
+    "crane_route_grouped": [P, I, P, P, I, I, I, I, I, I, P],
+    "crane_gated_activation": [I, P, P, I, L, P, I, I, P, I, I, I, I, P],
+    "crane_conv_delta_prep": [I, P, P, I, L, I, P, P, P, P, I, P, L, L, P, I, P, P, P, I, I, I, I, I, I, I, F, F, P, P],
+    "crane_decay_gate_prep": [I, P, P, I, L, I, P, P, P, I, F, F, P, I, I, I, I, I, P],
+    "crane_matrix_state_plan": [I, P, P],
+    "crane_matrix_state_scan": [P, I, I, I, I, I, I, I, I, I, P, P, P, I, P, L, P, I, I, I, I, P, P],
+    "crane_head_norm_gate": [I, P, P, P, I, L, I, I, P, P, F, P, I, I, I, P],
+    "crane_head_talk_mix": [I, P, P, P, P, I, I, I, I, I, P],
+    "crane_pair_norm_mean": [I, P, P, I, L, P, P, I, L, P, P, F, P, I, I, P],
     "crane_delta_rule_prep": [I, P, P, I, L, I, P, P, P, P, P, I, I, I, I, F, F, P],
     "crane_delta_rule_scan": [I, P, P, I, L, I, P, P, P, P, I, P, P, F, P, P, P, I, I, I, I, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
@@ -337,18 +348,22 @@ class Kernels:
                                               self._stream(logits)), "route_topk")
 
     def projection_norm_cache(self, qkv: Act, cols, positions, tok_entry, block_table, page_size, q_norm_w,
-                              k_norm_w, eps, q_out, k_pool, v_pool, nq, nkv, d, dv, err) -> None:
+                              k_norm_w, eps, q_out, k_pool, v_pool, nq, nkv, d, dv, err, cos=None, sin=None,
+                              rot_dims: int = 0, q_head_scale=None) -> None:
         """Rows [q | k | v] of a merged projection: q and k RMS-normed over all their heads at once
         (weights [nq d], [nkv d] or None), q written to ``q_out`` [n, nq, D], k and v into the
         token's place in the pools [pages, nkv, page_size, D / Dv], zero-filled where the pools'
-        rows are wider than d / dv."""
+        rows are wider than d / dv.  ``cos`` / ``sin`` float [positions, rot_dims / 2]: the leading
+        ``rot_dims`` elements of every query and key head are rotated by the token's position, element
+        i with i + rot_dims / 2; ``q_head_scale`` float [nq]: one factor per query head."""
         whole, parts, n_parts, stride = _split(qkv)
         self._check(self.lib.crane_projection_norm_cache(
             _dt(q_out.dtype), whole, parts, n_parts, stride, int(cols), positions.data_ptr(), tok_entry.data_ptr(),
             block_table.data_ptr(), block_table.shape[1], k_pool.shape[0], page_size, _ptr(q_norm_w),
             _ptr(k_norm_w), float(eps), q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), q_out.shape[0],
-            nq, nkv, d, dv, k_pool.shape[3], v_pool.shape[3], err.data_ptr(), self._stream(q_out)),
-            "projection_norm_cache")
+            nq, nkv, d, dv, k_pool.shape[3], v_pool.shape[3], _ptr(cos), _ptr(sin),
+            cos.shape[0] if cos is not None else 0, int(rot_dims) if cos is not None else 0, _ptr(q_head_scale),
+            err.data_ptr(), self._stream(q_out)), "projection_norm_cache")
 
     def delta_rule_max_dim(self) -> int:
         self.lib.crane_delta_rule_max_dim.restype = c_int
@@ -380,6 +395,106 @@ class Kernels:
             float(norm_eps), out.data_ptr(), _ptr(o_raw), _ptr(tok_entry), out.shape[0],
             int(col_blocks) if o_raw is not None and tok_entry is not None else 1, kv_len.shape[0], heads, d,
             err.data_ptr(), self._stream(out)), "delta_rule_scan")
+
+    # ---- several residual streams, grouped routing, gated experts ----------
+    def streams_norm(self, streams, x_first, y: Optional[Act], mix, outw, inw, g, eps: float, out, rows=None) -> None:
+        """``streams`` float [R, n, hidden].  With ``y`` (a sublayer's result): x_t <- sum_s mix[s, t] x_s
+        + outw[t] y for all t at once.  ``x_first`` float [n, hidden]: every stream starts as it (the
+        embedding output) instead.  Then out = u / rms(u) * g[0] with u = sum_t inw[t] x_t (``inw`` None:
+        the plain sum).  With ``rows`` only those rows are read and no stream is written."""
+        whole, parts, n_parts, stride = (None, None, 0, 0) if y is None else _split(y)
+        self._check(self.lib.crane_streams_norm(
+            _dt(out.dtype), streams.data_ptr(), streams.stride(0), streams.shape[0], _ptr(x_first), whole, parts,
+            n_parts, stride, _ptr(mix), _ptr(outw), _ptr(inw), g.data_ptr(), _ptr(rows), out.data_ptr(),
+            out.shape[0], streams.shape[2], float(eps), self._stream(out)), "streams_norm")
+
+    def route_grouped(self, z, correction, route, experts: int, top: int, groups: int, keep: int,
+                      shared_gate: bool) -> None:
+        """Per row of float ``z`` [n, >= experts (+ 1)]: scores = softmax over the experts; the ``top`` largest
+        of score + correction among the experts of the ``keep`` best of ``groups`` groups are chosen;
+        ``route`` [n, experts (+ 1)] gets their scores (zero elsewhere) and, ``shared_gate``, the
+        sigmoid of column ``experts`` behind them."""
+        assert z.dtype == torch.float32 and z.stride(1) == 1 and route.is_contiguous()
+        self._check(self.lib.crane_route_grouped(
+            z.data_ptr(), z.stride(0), _ptr(correction), route.data_ptr(), z.shape[0], int(experts), int(top),
+            int(groups), int(keep), 1 if shared_gate else 0, self._stream(z)), "route_grouped")
+
+    def gated_activation(self, gu: Act, out, route=None, experts: int = 0, per_expert: int = 0,
+                         routed_cols: int = 0, shared_gate: bool = False) -> None:
+        """out[t, c] = silu(gu[t, c]) * gu[t, cols + c], times the column's routing weight:
+        ``route[t, c // per_expert]`` for c < routed_cols, behind them ``route[t, experts]``
+        (``shared_gate``) or 1."""
+        whole, parts, n_parts, stride = _split(gu)
+        self._check(self.lib.crane_gated_activation(
+            _dt(out.dtype), whole, parts, n_parts, stride, out.data_ptr(), out.shape[0], out.shape[1], _ptr(route),
+            int(experts), int(per_expert), int(routed_cols), 1 if shared_gate else 0, self._stream(out)),
+            "gated_activation")
+
+    # ---- recurrences with a matrix state per head -----------------------
+    def matrix_state_plan(self, dk: int):
+        """(rows per lane, lanes per column) of the scan for keys of ``dk`` elements; the state of a head
+        takes rows * lanes * dv floats.  (0, 0): wider than the kernel takes."""
+        from ctypes import byref
+        r, l = c_int(0), c_int(0)
+        self.lib.crane_matrix_state_plan(int(dk), byref(r), byref(l))
+        return r.value, l.value
+
+    def conv_delta_prep(self, proj: Act, cols, ctx, state, conv_off, conv_w, taps, a_log, dt_bias, aux, H, G, d, dv,
+                        key_eps, q_scale, err, dtype) -> None:
+        """Rows [q | k | v | gate | b | a] of a merged projection -> ``aux`` rows [q | k | v | w | beta] in
+        32-bit: q, k, v through their short convolutions (weights ``conv_w`` [channels, taps]) and silu,
+        q and k to unit length per head (q times ``q_scale``), w = exp(-exp(a_log) softplus(a + dt_bias)),
+        beta = sigmoid(b).  The convolutions' last taps - 1 inputs live in ``state`` [slots, floats] at
+        ``conv_off`` and are replaced by a second kernel."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_conv_delta_prep(
+            _dt(dtype), whole, parts, n_parts, stride, int(cols), ctx.tok_entry.data_ptr(), ctx.cu_q.data_ptr(),
+            ctx.kv_len.data_ptr(), ctx.slots.data_ptr(), state.shape[0], state.data_ptr(), state.stride(0),
+            int(conv_off), conv_w.data_ptr(), int(taps), a_log.data_ptr(), dt_bias.data_ptr(), aux.data_ptr(),
+            aux.shape[1], aux.shape[0], ctx.kv_len.shape[0], H, G, d, dv, float(key_eps), float(q_scale),
+            err.data_ptr(), self._stream(aux)), "conv_delta_prep")
+
+    def decay_gate_prep(self, proj: Act, cols, tok_entry, a2t, bias, inv_tau, q_scale, aux, H, d, dv, dtype) -> None:
+        """Rows [q | k | v | gate | low] -> ``aux`` rows [q * q_scale | k | v | w] in 32-bit with
+        w = sigmoid(low a2t + bias)^inv_tau per key channel."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_decay_gate_prep(
+            _dt(dtype), whole, parts, n_parts, stride, int(cols), tok_entry.data_ptr(), a2t.data_ptr(),
+            bias.data_ptr(), a2t.shape[0], float(inv_tau), float(q_scale), aux.data_ptr(), aux.shape[1],
+            aux.shape[0], H, d, dv, self._stream(aux)), "decay_gate_prep")
+
+    def matrix_state_scan(self, aux, offs, w_vec: bool, delta: bool, qk_rep: int, ctx, state, o_raw, H, dk, dv,
+                          err) -> None:
+        """The recurrence S <- diag(w) S; u = beta (v - S^T k) (``delta``) or v; S <- S + k u^T; o = S^T q
+        over every entry's tokens, from and to ``state`` [slots, floats] (its leading H * rows * lanes * dv
+        floats).  ``offs``: columns of q, k, v, w, beta in ``aux``; ``o_raw`` float [n, H dv]."""
+        self._check(self.lib.crane_matrix_state_scan(
+            aux.data_ptr(), aux.shape[1], *[int(o) for o in offs], 1 if w_vec else 0, 1 if delta else 0, int(qk_rep),
+            ctx.cu_q.data_ptr(), ctx.kv_len.data_ptr(), ctx.slots.data_ptr(), state.shape[0], state.data_ptr(),
+            state.stride(0), o_raw.data_ptr(), ctx.kv_len.shape[0], H, dk, dv, err.data_ptr(),
+            self._stream(o_raw)), "matrix_state_scan")
+
+    def head_norm_gate(self, o_raw, proj: Act, cols, gate_off, tok_entry, norm_w, eps, out, H, dv) -> None:
+        """out = o_raw / rms(o_raw per head) * norm_w * silu(gate columns of ``proj``)."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_head_norm_gate(
+            _dt(out.dtype), o_raw.data_ptr(), whole, parts, n_parts, stride, int(cols), int(gate_off),
+            tok_entry.data_ptr(), norm_w.data_ptr(), float(eps), out.data_ptr(), out.shape[0], H, dv,
+            self._stream(out)), "head_norm_gate")
+
+    def head_talk_mix(self, cross, talk, tok_entry, out, H, G, dv, out_head) -> None:
+        """out[t, h] = sum_g talk[h, g] cross[t, g, h // (H / G)]; heads ``out_head`` apart in ``out``."""
+        self._check(self.lib.crane_head_talk_mix(
+            _dt(out.dtype), cross.data_ptr(), talk.data_ptr(), tok_entry.data_ptr(), out.data_ptr(), out.shape[0],
+            H, G, dv, int(out_head), self._stream(out)), "head_talk_mix")
+
+    def pair_norm_mean(self, a: Act, b: Act, wa, wb, eps, out) -> None:
+        """out = (a / rms(a) * wa + b / rms(b) * wb) / 2 per row."""
+        aw, ap, an, astr = _split(a)
+        bw, bp, bn, bstr = _split(b)
+        self._check(self.lib.crane_pair_norm_mean(
+            _dt(out.dtype), aw, ap, an, astr, bw, bp, bn, bstr, wa.data_ptr(), wb.data_ptr(), float(eps),
+            out.data_ptr(), out.shape[0], out.shape[1], self._stream(out)), "pair_norm_mean")
 
     # ---- matrix product on the FP32 cores ------------------------------
     def gemm_simt(self, a, w, bias, out) -> None:
@@ -564,18 +679,22 @@ class Kernels:
     # ---- attention ------------------------------------------------------
     def paged_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table,
                              page_size, nq, nkv, d, window, scale, err, dv=None, v_stride=None,
-                             sink: bool = False) -> None:
+                             sink: bool = False, out_cross=None) -> None:
         """``dv``: width of a value row (default: the keys'), ``v_stride``: elements
         between value rows (default ``dv``).  With ``v_pool`` the key pool itself and
         ``v_stride == d`` the values are the leading ``dv`` columns of the key rows.
-        ``sink``: the softmax has one more candidate of score 0 that has no value."""
+        ``sink``: the softmax has one more candidate of score 0 that has no value.
+        ``out_cross`` float [n, nq, nkv, dv]: every query head's weights are applied to the values
+        of EVERY key/value head (its scores still come from its own group's keys) and written there
+        instead of ``out`` (which may be None), for attention whose heads exchange their weights."""
         dv = d if dv is None else int(dv)
         v_stride = dv if v_stride is None else int(v_stride)
         self._check(self.lib.crane_paged_attention_simt(
-            _dt(q.dtype), q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+            _dt(q.dtype), q.data_ptr(), _ptr(out), k_pool.data_ptr(), v_pool.data_ptr(),
             positions.data_ptr(), tok_entry.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, dv, v_stride,
-            int(window), float(scale), 1 if sink else 0, err.data_ptr(), self._stream(q)), "paged_attention_simt")
+            int(window), float(scale), 1 if sink else 0, _ptr(out_cross), err.data_ptr(), self._stream(q)),
+            "paged_attention_simt")
 
     @staticmethod
     def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64, max_keys: int = 1 << 30) -> int:

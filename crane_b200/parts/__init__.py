@@ -2,7 +2,8 @@
 from .base import (CacheNeed, LayerCache, Part, Workspace, block_class, build_part, part_class,
                    register_block, register_part)
 from .runtime import DeviceFault, Runtime
-from . import attention, block, delta_rule, embedding, feed_forward, latent_attention, norm, position   # register the parts
+from . import (attention, block, delta_rule, embedding, feed_forward, latent_attention, norm, pair, position,   # register the parts
+               recurrent)
 from .model import DecoderModel, model_manifest
 
 __all__ = ["CacheNeed", "LayerCache", "Part", "Workspace", "block_class", "build_part",

@@ -290,7 +290,8 @@ class SinkAttention(Part):
         return rt.linear(o, self.o_w, None, "attn_out")
 
 
-def sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, scale, sink, max_splits) -> int:
+def sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, scale, sink, max_splits,
+                           cross: bool = False) -> int:
     """Attention of q [n, H, D] over pools of head size D with the warp-level kernels: entries of
     one token through the split-KV decode kernel where that pays, the others through the prefill
     kernel.  Returns the launches."""
@@ -317,3 +318,96 @@ def sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, scal
     k.paged_prefill_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size, tiles, H, G, D,
                               window, scale, rt.err, skip_single=bool(singles), sink=sink)
     return launches + 1
+
+
+@register_part("mixer", "talking_attention")
+class TalkingAttention(Part):
+    """Grouped-query attention whose heads exchange their softmax weights: scores of head h are
+    q_h . k_(h // (H / G)) * scale * temp[h], causal softmax, then w'_h = sum_g talk[h, g] w_g, and head h
+    applies w'_h to the values of its own key/value head.  Rotary positions on the leading
+    ``rotary_dim`` elements of every query and key head (element i with i + rotary_dim / 2).
+
+    The mixed weights are never formed.  o_h = sum_g talk[h, g] (w_g V_(kv of h)): every query head's own
+    weights are applied to the values of EVERY key/value head (H x G results per token, 32-bit), and a
+    small kernel mixes those with ``talk``.  The softmax itself stays an ordinary one per head.
+
+    params: ``hidden_size``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``rotary_dim`` (0: none),
+    ``position`` (a PartSpec of kind position whose tables have rotary_dim / 2 columns, or None),
+    ``window`` (0: every earlier position), ``head_dim`` (bfloat16: the common head size keys and values are
+    stored at; 0: as wide as they are), ``names``.  Tensors: q [H dim, hidden], k [G dim, hidden],
+    v [G vdim, hidden], o [hidden, H vdim], and in 32-bit talk [H, H], temp [H]."""
+    kind = "mixer"
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "talk": "talk", "temp": "temp"}
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        w, H, G, d, m = (int(a[k]) for k in ("hidden_size", "heads", "kv_heads", "dim", "vdim"))
+        nm = dict(cls.NAMES, **(a.get("names") or {}))
+        return {p + nm["q"]: TensorSpec((H * d, w)), p + nm["k"]: TensorSpec((G * d, w)),
+                p + nm["v"]: TensorSpec((G * m, w)), p + nm["o"]: TensorSpec((w, H * m)),
+                p + nm["talk"]: TensorSpec((H, H), "float32", "eye"), p + nm["temp"]: TensorSpec((H,), "float32", "scale")}
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        self.w, self.H, self.G, self.d, self.m = (int(a[k]) for k in ("hidden_size", "heads", "kv_heads", "dim", "vdim"))
+        nm = dict(self.NAMES, **(a.get("names") or {}))
+        if self.H % self.G:
+            raise ValueError(f"{p}: {self.H} query heads are not a multiple of {self.G} key/value heads")
+        if self.d > 1024 or self.m > 512:
+            raise ValueError(f"{p}: heads of {self.d} / {self.m} elements are wider than the attention kernels "
+                             "take (1024 / 512)")
+        self.scale = float(a["scale"])
+        self.window = int(a.get("window") or 0)
+        self.rot = int(a.get("rotary_dim") or 0)
+        self.position = build_part(a["position"]) if self.rot and a.get("position") is not None else None
+        if self.rot and self.position is None:
+            raise ValueError(f"{p}: rotary_dim {self.rot} needs a position part")
+        if self.position is not None:
+            self.position.load(weights, rt)
+        self.qkv_w = torch.cat([weights.pop(p + nm[n]) for n in ("q", "k", "v")], dim=0).contiguous()
+        self.cols = self.qkv_w.shape[0]
+        self.o_w = weights[p + nm["o"]]
+        self.talk, self.temp = weights[p + nm["talk"]], weights[p + nm["temp"]]
+        # bfloat16: keys and values at one common head size that the warp-level kernels are compiled for
+        # (zero-filled columns add nothing to a score; value columns beyond vdim are never read back)
+        self.store = int(a.get("head_dim") or 0) if not rt.exact else 0
+        if self.store and not (rt.kernels.prefill_attention_supports(self.store, self.H * self.G, self.G)
+                               and getattr(rt.kernels, "mma_attention_takes_cross", False)):
+            self.store = 0
+        self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "64"))
+
+    def cache_need(self) -> CacheNeed:
+        if self.store:
+            return CacheNeed("kv", kv_heads=self.G, head_dim=self.store, window=self.window)
+        return CacheNeed("kv", kv_heads=self.G, head_dim=self.d, window=self.window, v_head_dim=self.m)
+
+    def forward(self, h, ctx, cache, rt, hold: bool = False):
+        n, k = h.shape[0], rt.kernels
+        H, G, d, m = self.H, self.G, self.d, self.m
+        qkv = rt.linear(h, self.qkv_w, None, "attn_qkv")
+        table = ctx.block_tables[cache.group]
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.tables(rt, ctx.max_positions)
+            if cos.shape[1] * 2 != self.rot:
+                raise ValueError(f"{self.prefix}: the position encoding gives tables for a rotated width of "
+                                 f"{cos.shape[1] * 2}, the mixer rotates {self.rot}")
+        D = self.store or d
+        q = rt.ws.get("attn_q", n, H * D, rt.dtype)
+        k.projection_norm_cache(qkv, self.cols, ctx.positions, ctx.tok_entry, table, cache.page_size, None, None, 0.0,
+                                q, cache.k, cache.v, H, G, d, m, rt.err, cos=cos, sin=sin, rot_dims=self.rot,
+                                q_head_scale=self.temp)
+        Dv = self.store or m
+        cross = rt.ws.get("attn_cross", n, H * G * Dv, torch.float32)
+        if not self.store:
+            k.paged_attention_simt(q, None, cache.k, cache.v, ctx.positions, ctx.tok_entry, table, cache.page_size,
+                                   H, G, d, self.window, self.scale, rt.err, dv=m, v_stride=m, out_cross=cross)
+            rt.launches += 1
+        else:
+            rt.launches += sink_attention_kernels(k, rt, ctx, q, cross, cache, table, H, G, D, self.window, self.scale,
+                                                  False, self.max_splits, cross=True)
+        o = rt.ws.get("attn_o", n, H * m, rt.dtype)
+        k.head_talk_mix(cross, self.talk, ctx.tok_entry, o, H, G, Dv, m)
+        rt.launches += 2
+        return rt.linear(o, self.o_w, None, "attn_out", hold=hold)

@@ -76,7 +76,10 @@ class CacheNeed:
     ``values_in_keys``: the values are the leading ``v_head_dim`` columns of the key
     rows (latent attention): there is no V pool, ``LayerCache.v`` is the K pool.
     ``kind == "state"``: one tensor of ``state_shape`` / ``state_dtype`` in the
-    request's slot.  ``kind == "none"``: nothing (or another layer's cache)."""
+    request's slot.  ``kind == "none"``: nothing (or another layer's cache).
+    ``kind == "multi"``: several of the above at once (``parts``), for a mixer made of
+    mixers (pages for one, a state for another); its ``LayerCache.parts`` holds a
+    ``LayerCache`` for each, in order."""
     kind: str = "none"
     kv_heads: int = 0
     head_dim: int = 0
@@ -85,6 +88,13 @@ class CacheNeed:
     state_dtype: torch.dtype = torch.float32
     v_head_dim: int = 0
     values_in_keys: bool = False
+    parts: Tuple["CacheNeed", ...] = ()
+
+    def flat(self) -> Tuple["CacheNeed", ...]:
+        """The needs this one stands for: itself, or its parts (and theirs) in order."""
+        if self.kind != "multi":
+            return (self,)
+        return tuple(f for p in self.parts for f in p.flat())
 
     @property
     def value_dim(self) -> int:
@@ -105,6 +115,7 @@ class LayerCache:
     v: Optional[torch.Tensor] = None
     page_size: int = 0
     state: Optional[torch.Tensor] = None
+    parts: Tuple["LayerCache", ...] = ()      # of a ``multi`` need: one per part
 
 
 class Part:

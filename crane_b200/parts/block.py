@@ -12,6 +12,11 @@ token input joins the stream.
 ``parallel_depth_average``: both branches read norms of the same x, their sum
 is added once, and what the next layer reads is a weighted sum of all layer
 results so far.
+
+``hyper_connections``: R residual streams, all equal to the embedding output at the
+start; a sublayer reads u = sum_s in[s] x_s through its norm, and its result y joins
+all streams at once, x_t <- sum_s mix[s][t] x_s + out[t] y.  The model's last norm
+reads the plain sum of the streams.
 """
 from __future__ import annotations
 
@@ -19,7 +24,7 @@ import torch
 
 from ..weights.loader import TensorSpec
 from .base import Part, build_part, register_block, register_part
-from .norm import BranchSum, add_normed, combine_and_norm
+from .norm import BranchSum, StreamUpdate, add_normed, combine_and_norm
 
 
 @register_block("prenorm_residual")
@@ -185,3 +190,61 @@ class SandwichResidualBlock:
         if self.side is not None:
             self.side.forward(x, raw, ctx, rt)
         return None
+
+
+@register_part("connect", "stream_connection")
+class StreamConnection(Part):
+    """How one sublayer reads and writes ``streams`` residual streams: ``in`` [R] (what it reads),
+    ``mix`` [R, R] indexed [from, to] and ``out`` [R] (how its result joins).  params: ``streams``,
+    ``stored`` (False: one stream and the plain residual sum, in = mix = out = 1, no tensors),
+    ``names``.  Tensors kept float."""
+    kind = "connect"
+    NAMES = {"in": "in", "mix": "mix", "out": "out"}
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        if not a.get("stored", True):
+            return {}
+        r = int(a["streams"])
+        nm = dict(cls.NAMES, **(a.get("names") or {}))
+        return {p + nm["in"]: TensorSpec((r,), "float32", "mix"), p + nm["out"]: TensorSpec((r,), "float32", "scale"),
+                p + nm["mix"]: TensorSpec((r, r), "float32", "eye")}
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        self.streams = int(a["streams"])
+        if not a.get("stored", True):
+            if self.streams != 1:
+                raise ValueError(f"{p}: {self.streams} streams need their tensors")
+            one = torch.ones(1, dtype=torch.float32, device=rt.device)
+            self.inw, self.mix, self.out = one, one.clone(), one.clone()
+            return
+        nm = dict(self.NAMES, **(a.get("names") or {}))
+        self.inw, self.mix, self.out = weights[p + nm["in"]], weights[p + nm["mix"]], weights[p + nm["out"]]
+
+
+@register_block("hyper_connections")
+class HyperConnectionBlock:
+    """parts: ``norm1`` (a ``scalar_rms_norm``), ``mixer``, ``connect1``; unless the layer has no
+    feed-forward ``norm2``, ``ffn``, ``connect2``.  Every update of the streams is one kernel with the
+    norm that reads them next, so the block hands its last result on as a ``StreamUpdate``."""
+
+    def __init__(self, layer_spec):
+        p = layer_spec.parts
+        self.norm1, self.mixer, self.connect1 = (build_part(p[k]) for k in ("norm1", "mixer", "connect1"))
+        self.ffn = build_part(p["ffn"]) if "ffn" in p else None
+        self.norm2 = build_part(p["norm2"]) if self.ffn is not None else None
+        self.connect2 = build_part(p["connect2"]) if self.ffn is not None else None
+
+    def parts(self):
+        return [q for q in (self.norm1, self.mixer, self.connect1, self.norm2, self.ffn, self.connect2)
+                if q is not None]
+
+    def forward(self, x, pending, ctx, cache, rt):
+        h = self.norm1.forward(x, pending, rt, connect=self.connect1)
+        a = self.mixer.forward(h, ctx, cache, rt)
+        if self.ffn is None:
+            return StreamUpdate(a, self.connect1)
+        h2 = self.norm2.forward(x, StreamUpdate(a, self.connect1), rt, name="normed2", connect=self.connect2)
+        return StreamUpdate(self.ffn.forward(h2, ctx, rt), self.connect2)

@@ -15,16 +15,17 @@ from .base import Part, register_part
 
 @register_part("embed", "token_embedding")
 class TokenEmbedding(Part):
-    """params: ``vocab_size``, ``hidden_size``.  Tensor: ``<prefix>weight`` [V,H]."""
+    """params: ``vocab_size``, ``hidden_size``, ``table`` (tensor name behind the prefix; default
+    "weight").  Tensor [V,H]."""
     kind = "embed"
 
     @classmethod
     def manifest(cls, spec):
-        return {spec.prefix + "weight": TensorSpec((spec.params["vocab_size"],
-                                                    spec.params["hidden_size"]))}
+        return {spec.prefix + (spec.params.get("table") or "weight"): TensorSpec((spec.params["vocab_size"],
+                                                                                  spec.params["hidden_size"]))}
 
     def load(self, weights, rt):
-        self.table = weights[self.prefix + "weight"]
+        self.table = weights[self.prefix + (self.params.get("table") or "weight")]
 
     def forward(self, tokens, x, rt, deferred=None):
         """Writes the float residual rows ``x`` [N,H] for int32 ``tokens`` [N].
@@ -37,19 +38,20 @@ class TokenEmbedding(Part):
 @register_part("head", "lm_head")
 class LMHead(Part):
     """params: ``vocab_size``, ``hidden_size``, ``tied_to`` (name of the tensor
-    it shares, or None).  Tensor when untied: ``<prefix>weight`` [V,H]."""
+    it shares, or None), ``tensor`` (its own tensor's name behind the prefix; default
+    "weight").  Tensor when untied [V,H]."""
     kind = "head"
 
     @classmethod
     def manifest(cls, spec):
         if spec.params.get("tied_to"):
             return {}
-        return {spec.prefix + "weight": TensorSpec((spec.params["vocab_size"],
-                                                    spec.params["hidden_size"]))}
+        return {spec.prefix + (spec.params.get("tensor") or "weight"): TensorSpec((spec.params["vocab_size"],
+                                                                                   spec.params["hidden_size"]))}
 
     def load(self, weights, rt):
         tied = self.params.get("tied_to")
-        self.weight = weights[tied] if tied else weights[self.prefix + "weight"]
+        self.weight = weights[tied] if tied else weights[self.prefix + (self.params.get("tensor") or "weight")]
 
     def forward(self, h, rt):
         # wanted rows are few when serving; the buffer grows if a caller wants more

@@ -173,3 +173,85 @@ class RoutedExperts(Part):
         k.ffn_activation(up, act, self.act, route, self.F, self.E * self.F)
         rt.launches += 2
         return rt.linear(act, self.down, None, "experts_down")
+
+
+@register_part("ffn", "grouped_experts")
+class GroupedExperts(Part):
+    """A mixture of gated feed-forwards down_e(silu(gate_e(h)) * up_e(h)).  The router's logits
+    z = W_r h are formed in 32-bit; scores s = softmax(z) over ALL experts; an expert's choice score
+    is s plus a learnt correction; experts come in ``groups`` equal groups of neighbours, a group
+    counts as much as its best choice score, and only experts of the ``keep`` best groups can be
+    chosen; the ``top`` largest choice scores among those are chosen (ties to the lower index) and
+    weighted by their scores s, without the correction and without renormalising.  An optional shared
+    expert of the same form runs for every token and is added, times sigmoid(w_sg . h) if it has a gate.
+    params: ``hidden_size``, ``experts``, ``top``, ``groups``, ``keep``, ``expert_size``, ``shared_size``
+    (0: none), ``correction`` (tensor name or None), ``shared_gate`` (tensor name or None), ``names``.
+    Tensors: router [E,H]; correction [E] (float); per expert gate, up [F,H], down [H,F]; shared gate,
+    up [Fs,H], down [H,Fs]; shared_gate [1,H].
+
+    All experts' gate matrices (and the shared one's), then all up matrices, are ONE matrix, and so are
+    the down matrices: a step is two products with the activation between them, which multiplies
+    every expert's columns by the token's routing weight (zero for experts that it did not choose).
+    The router's matrix carries the shared gate's row behind the experts'.  The result of a token does
+    not depend on what else is in the batch."""
+    kind = "ffn"
+    NAMES = {"router": "router", "expert": "e{e}.", "shared": "shared.", "gate": "gate", "up": "up", "down": "down"}
+
+    @classmethod
+    def _sizes(cls, a):
+        return (int(a["hidden_size"]), int(a["experts"]), int(a["expert_size"]), int(a.get("shared_size") or 0))
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        nm = dict(cls.NAMES, **(a.get("names") or {}))
+        h, E, F, Fs = cls._sizes(a)
+        m = {p + nm["router"]: TensorSpec((E, h))}
+        if a.get("correction"):
+            m[p + a["correction"]] = TensorSpec((E,), "float32", "offset")
+        for e in range(E):
+            q = p + nm["expert"].format(e=e)
+            m[q + nm["gate"]] = TensorSpec((F, h))
+            m[q + nm["up"]] = TensorSpec((F, h))
+            m[q + nm["down"]] = TensorSpec((h, F))
+        if Fs:
+            q = p + nm["shared"]
+            m[q + nm["gate"]] = TensorSpec((Fs, h))
+            m[q + nm["up"]] = TensorSpec((Fs, h))
+            m[q + nm["down"]] = TensorSpec((h, Fs))
+            if a.get("shared_gate"):
+                m[p + a["shared_gate"]] = TensorSpec((1, h))
+        return m
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        nm = dict(self.NAMES, **(a.get("names") or {}))
+        _, self.E, self.F, self.Fs = self._sizes(a)
+        self.top, self.groups = int(a["top"]), int(a.get("groups") or 1)
+        self.keep = int(a.get("keep") or self.groups)
+        if not 0 < self.top <= self.E or self.E % self.groups or not 0 < self.keep <= self.groups:
+            raise ValueError(f"{p}: {self.top} of {self.E} experts in {self.groups} groups ({self.keep} kept) cannot be chosen")
+        self.correction = weights[p + a["correction"]] if a.get("correction") else None
+        self.shared_gate = bool(self.Fs and a.get("shared_gate"))
+        router = [weights.pop(p + nm["router"])]
+        if self.shared_gate:
+            router.append(weights.pop(p + a["shared_gate"]).reshape(1, -1))
+        self.router = torch.cat(router, dim=0).contiguous()           # [E (+ 1), H]
+        names = [p + nm["expert"].format(e=e) for e in range(self.E)] + ([p + nm["shared"]] if self.Fs else [])
+        gates = [weights.pop(q + nm["gate"]) for q in names]
+        ups = [weights.pop(q + nm["up"]) for q in names]
+        downs = [weights.pop(q + nm["down"]) for q in names]
+        self.gate_up = torch.cat(gates + ups, dim=0).contiguous()      # [2 (E F + Fs), H]: gates, then ups
+        self.down = torch.cat(downs, dim=1).contiguous()               # [H, E F + Fs]
+        self.inter = self.down.shape[1]
+
+    def forward(self, h, ctx, rt):
+        n, k = h.shape[0], rt.kernels
+        z = rt.linear(h, self.router, None, "router_logits", out_dtype=torch.float32)
+        route = rt.ws.get("route_weights", n, self.E + (1 if self.shared_gate else 0), torch.float32)
+        k.route_grouped(z, self.correction, route, self.E, self.top, self.groups, self.keep, self.shared_gate)
+        gu = rt.linear(h, self.gate_up, None, "experts_gate_up")
+        act = rt.ws.get("experts_act", n, self.inter, rt.dtype)
+        k.gated_activation(gu, act, route, self.E, self.F, self.E * self.F, self.shared_gate)
+        rt.launches += 2
+        return rt.linear(act, self.down, None, "experts_down")

@@ -85,7 +85,8 @@ class DecoderModel:
     def state_graph_safe(self) -> bool:
         """Whether every mixer that keeps per-request state bears graphs and padding."""
         keepers = [b.mixer for b in self.blocks] + ([self.embed] if hasattr(self.embed, "cache_need") else [])
-        return all(getattr(p, "state_graph_safe", False) for p in keepers if p.cache_need().kind == "state")
+        return all(getattr(p, "state_graph_safe", False) for p in keepers
+                   if any(f.kind == "state" for f in p.cache_need().flat()))
 
     def forward(self, ctx, caches: List[LayerCache]) -> torch.Tensor:
         """Runs the step's tokens through the schedule (``caches``: one entry

@@ -121,3 +121,57 @@ class LayerNorm(Part):
     def forward(self, x, delta, rt, rows=None, name="normed"):
         """As ``RMSNorm.forward``; ``delta`` may also be a ``BranchSum``."""
         return combine_and_norm(x, delta, self, None, rt, rows, (name, name + "2"))[0]
+
+
+class StreamUpdate:
+    """What a block of several residual streams hands on instead of adding it: a sublayer's result
+    ``y`` and the ``stream_connection`` part that says how it joins the streams.  The norm that
+    reads the streams next does the update in its own kernel."""
+
+    def __init__(self, y, connect):
+        self.y, self.connect = y, connect
+
+
+def residual_streams(rt, n: int, size: int, streams: int):
+    """The step's residual streams, float [streams, n, size], in the workspace."""
+    import torch
+    buf = rt.ws.get("residual_streams", streams * n, size, torch.float32, cap=streams * rt.ws.max_rows)
+    return buf.view(streams, n, size)
+
+
+@register_part("norm", "scalar_rms_norm")
+class ScalarRMSNorm(Part):
+    """RMS norm with ONE learnt number for all coordinates, reading ``streams`` residual streams:
+    u = sum_t in[t] x_t (``connect`` given: the reading sublayer's weights; else the plain sum),
+    y = u / sqrt(mean(u^2) + eps) * g.  An update of the streams that is still pending (a
+    ``StreamUpdate``) is applied first, in the same kernel.  params: ``size``, ``eps``, ``weight``
+    (tensor name behind the prefix), ``streams``, ``gain`` (a constant folded into g: a model's
+    logit scale, for its last norm).  Tensor [] (a single number), kept float."""
+    kind = "norm"
+
+    @classmethod
+    def manifest(cls, spec):
+        return {spec.prefix + spec.params.get("weight", "weight"): TensorSpec((), "float32", "scale")}
+
+    def load(self, weights, rt):
+        g = weights[self.prefix + self.params.get("weight", "weight")].reshape(1)
+        self.g = (g * float(self.params.get("gain") or 1.0)).contiguous()
+        self.eps = float(self.params["eps"])
+        self.size = int(self.params["size"])
+        self.streams = int(self.params.get("streams") or 1)
+
+    def forward(self, x, pending, rt, rows=None, name="normed", connect=None):
+        """``x`` [n, size]: the embedding output, which every stream starts as when nothing is pending
+        and no layer has run (``pending`` None).  Returns the normed rows in the model dtype."""
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = rt.ws.get(name, n, self.size, rt.dtype)
+        streams = residual_streams(rt, x.shape[0], self.size, self.streams)
+        y = mix = outw = None
+        if isinstance(pending, StreamUpdate):
+            y, mix, outw = pending.y, pending.connect.mix, pending.connect.out
+        elif pending is not None:
+            raise TypeError("scalar_rms_norm reads residual streams; what is pending must be a StreamUpdate")
+        rt.kernels.streams_norm(streams, x if pending is None else None, y, mix, outw,
+                                connect.inw if connect is not None else None, self.g, self.eps, out, rows)
+        rt.launches += 1
+        return out

@@ -47,7 +47,7 @@ class TensorSpec:
     keep: str = "model"        # "model" | "float32" | "keep"
     # how random weights are drawn for it, where the name and ``keep`` do not say: "" (by name),
     # "scale" (1 + noise: a norm's weight), "offset" (noise: a bias), "mix" (weights of an average
-    # over the tensor's length), "unit" (numbers of order one)
+    # over the tensor's length), "unit" (numbers of order one), "eye" (a square matrix near the identity)
     init: str = ""
     # a dimension of -1 in ``shape`` is read from the stored tensor (a size that the configuration does
     # not state); ``free`` is what random weights take for it

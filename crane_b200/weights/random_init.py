@@ -46,6 +46,8 @@ def random_tensors(manifest: Dict[str, TensorSpec], seed: int, dtype: torch.dtyp
             out[name] = (1.0 + 0.5 * t) / t.numel()
         elif spec.init == "offset":
             out[name] = std * t
+        elif spec.init == "eye":
+            out[name] = torch.eye(shape[0], shape[1]) + std * t       # a mixing matrix near the identity
         elif spec.init == "unit":
             out[name] = 0.5 * t
         elif spec.keep == "float32":
