@@ -150,7 +150,7 @@ class DictSource:
 
 
 def _raw_bytes(t: torch.Tensor) -> bytes:
-    t = t.detach().contiguous().cpu()
+    t = t.detach().contiguous().cpu().reshape(-1)          # (a single number has no dimension to view)
     return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
 
 

@@ -300,3 +300,19 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], tokens, state: Optional[list] =
     x = scalar_norm(xs.sum(axis=0), w["final.norm"], eps)
     logits = (x @ w["head"].T) * float(cfg.get("logit_scale") or 1.0)
     return logits, np.stack(sums), state
+
+
+def logits_all(cfg: dict, w: Dict[str, np.ndarray], tokens) -> np.ndarray:
+    """Logits at every position of one sequence, [n, V]."""
+    return forward(cfg, w, list(tokens))[0]
+
+
+def greedy_generate(cfg: dict, w: Dict[str, np.ndarray], prompt: List[int], new_tokens: int) -> List[int]:
+    """The prompt and ``new_tokens`` more, each the largest logit's index (ties to the lower index);
+    the prompt in one call, then token by token from the carried state."""
+    toks = list(prompt)
+    logits, _, state = forward(cfg, w, toks)
+    for _ in range(new_tokens):
+        toks.append(int(np.argmax(logits[-1])))
+        logits, _, state = forward(cfg, w, toks[-1:], state, start=len(toks) - 1)
+    return toks
