@@ -792,6 +792,239 @@ def vodelix_workload(args, pk):
     return out
 
 
+def mufevik_config(like, layers):
+    """A Mufevik model with the width, layer count and vocabulary of the Hunyuan configuration `like`:
+    of every three layers one runs the gated delta rule (heads of 64 across the width, half as many
+    query/key heads, a convolution of four taps) and two run attention whose heads exchange their
+    weights (the other's head counts, heads of 128, half of each rotated) beside gated linear
+    attention (keys of 64, values of 128); every layer has eight experts of a quarter of the other's
+    inner size in four groups, two groups kept and two experts chosen, and a shared one; three streams."""
+    h, heads, kv = like["hidden_size"], like["num_attention_heads"], like["num_key_value_heads"]
+    ff = like["intermediate_size"]
+    left = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "rot": {"dims": 64, "base": 10000.0}}
+    right = {"heads": max(1, h // 256), "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 64}
+    delta = {"heads": h // 64, "kv_heads": max(1, h // 128), "dim": 64, "vdim": 64, "conv": 4}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    ls = [{"type": "delta" if i % 3 == 0 else "parallel",
+           "mixer": delta if i % 3 == 0 else {"left": left, "right": right}, "mlp": moe} for i in range(layers)]
+    return {"architecture": "Mufevik", "vocab": like["vocab_size"], "width": h, "norm": {"eps": 1e-5},
+            "streams": 3, "logit_scale": 1.0, "layers": ls}
+
+
+def mufevik_kernel_table(mcfg, vcfg, hcfg, pk, tokens, batch, context):
+    """Every kernel that only Mufevik runs beside the kernel of Vodelix (the engine's closest model)
+    that does the like job, each alone on synthetic operands of the two models' layer sizes (L2
+    flushed between repetitions), with the fraction of its roofline: algorithmic bytes over the
+    measured copy rate, or FLOPs over the measured bf16 rate, whichever takes longer."""
+    import math
+    from types import SimpleNamespace
+    import numpy as np
+    import torch
+    from crane_b200.kernels import get_kernels
+    K = get_kernels([128])
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    W, R = mcfg["width"], mcfg["streams"]
+    dl = next(l["mixer"] for l in mcfg["layers"] if l["type"] == "delta")
+    par = next(l["mixer"] for l in mcfg["layers"] if l["type"] == "parallel")
+    lt, rg = par["left"], par["right"]
+    vd = next(l["mixer"] for l in vcfg["layers"] if l["type"] == "general_delta")
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, like, ms, nbytes, flops, like_ms=0, like_bytes=0, like_flops=0):
+        def frac(ms_, b, f):
+            return round(max(b / hbm, f / peak) / (ms_ * 1e-3), 4)
+        rows.append({"kernel": name, "ms": round(ms, 4), "frac": frac(ms, nbytes, flops), "like": like,
+                     "like_ms": round(like_ms, 4) if like_ms else None,
+                     "like_frac": frac(like_ms, like_bytes, like_flops) if like_ms else None})
+
+    T = tokens
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=dev, dtype=torch.float32).to(dt)
+    f32 = torch.float32
+    # a sublayer's result joins the streams and the next norm reads them / the single stream's like
+    streams, y, o1 = rnd(R, T, W, dt=f32), rnd(T, W), torch.empty(T, W, device=dev, dtype=bf)
+    mix, outw, inw, g = rnd(R, R, dt=f32), rnd(R, dt=f32), rnd(R, dt=f32), rnd(1, dt=f32)
+    x, w = rnd(T, W, dt=f32), [rnd(W, dt=f32) for _ in range(2)]
+    t_m = _median_ms(lambda: K.streams_norm(streams, None, y, mix, outw, inw, g, 1e-5, o1), flush=flush)
+    t_v = _median_ms(lambda: K.add_normed_norm(x, y, w[0], 1e-5, w[1], 1e-5, o1), flush=flush)
+    add(f"streams_norm ({R} streams)", "add_normed_norm", t_m, T * W * (8 * R + 4), 0, t_v, T * W * 12, 0)
+    a2, b2 = rnd(T, W), rnd(T, W)
+    t_m = _median_ms(lambda: K.pair_norm_mean(a2, b2, w[0], w[1], 1e-5, o1), flush=flush)
+    add("pair_norm_mean", "add_normed_norm", t_m, T * W * 6, 0, t_v, T * W * 12, 0)
+    del streams, x, a2, b2
+    # the router and the activation between the experts' two products
+    moe = mcfg["layers"][0]["mlp"]
+    E, F, Fs = moe["router"]["experts"], moe["expert"]["ff"], moe["shared"]["ff"]
+    top, gc, gk = moe["router"]["top"], moe["router"]["groups"]["count"], moe["router"]["groups"]["keep"]
+    cols = E * F + Fs
+    z, corr = rnd(T, E + 1, dt=f32), rnd(E, dt=f32)
+    route = torch.empty(T, E + 1, device=dev)
+    t_m = _median_ms(lambda: K.route_grouped(z, corr, route, E, top, gc, gk, True), flush=flush)
+    idx, wt = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, device=dev)
+    route_v = torch.rand(T, E, device=dev)
+    t_v = _median_ms(lambda: K.route_topk(z[:, :E].contiguous(), route_v, idx, wt), flush=flush)
+    add("route_grouped", "route_topk", t_m, T * (E + 1) * 8, 0, t_v, T * E * 8, 0)
+    gu, act = rnd(T, 2 * cols), torch.empty(T, cols, device=dev, dtype=bf)
+    up = rnd(T, cols)
+    t_m = _median_ms(lambda: K.gated_activation(gu, act, route, E, F, E * F, True), flush=flush)
+    t_v = _median_ms(lambda: K.ffn_activation(up, act, "gelu", route_v, F, E * F), flush=flush)
+    add("gated_activation (silu gate x up x routing weight)", "ffn_activation (gelu x routing weight)", t_m,
+        T * cols * 6, 0, t_v, T * cols * 4, 0)
+    del gu, act, up
+    ps = 64
+    H, G, d = lt["heads"], lt["kv_heads"], lt["dim"]
+    dH, dG, dk, dv, taps = dl["heads"], dl["kv_heads"], dl["dim"], dl["vdim"], dl["conv"]
+    gH, gk_, gv_, rank = rg["heads"], rg["dim"], rg["vdim"], rg["decay_rank"]
+    vH, vdd, vR = vd["heads"], vd["dim"], vd["decay_rank"]
+    for kind, n_req, q_len, kv in (("prefill", 1, T, T), ("decode", batch, 1, context)):
+        blocks = -(-kv // ps)
+        pages = n_req * blocks
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(n_req, blocks)
+        cu_d = torch.from_numpy(np.arange(n_req + 1, dtype=np.int32) * q_len).to(dev)
+        kv_d = torch.from_numpy(np.full(n_req, kv, dtype=np.int32)).to(dev)
+        n = n_req * q_len
+        pos = torch.from_numpy(np.concatenate([np.arange(kv - q_len, kv, dtype=np.int32)] * n_req)).to(dev)
+        ent = torch.from_numpy(np.repeat(np.arange(n_req, dtype=np.int32), q_len)).to(dev)
+        slots = torch.arange(n_req, dtype=torch.int32, device=dev)
+        ctx = SimpleNamespace(tok_entry=ent, cu_q=cu_d, kv_len=kv_d, slots=slots)
+        # Vodelix: what prepares its recurrence, and the recurrence
+        hd = vH * vdd
+        pcols = 5 * hd + vR
+        proj = rnd(n, pcols)
+        w2, w0, ab, nw = rnd(vR, hd), rnd(hd, dt=f32), rnd(hd, dt=f32), rnd(hd, dt=f32)
+        aux = torch.empty(n, 3 * hd, device=dev)
+        vstate = torch.zeros(n_req, vH, vdd, vdd, device=dev)
+        od = torch.empty(n, hd, device=dev, dtype=bf)
+        prep_v = lambda: K.delta_rule_prep(proj, pcols, ent, w2, w0, ab, aux, vH, vdd, math.exp(-0.5), 1e-6, bf)
+        t_pv = _median_ms(prep_v, flush=flush)
+        prep_v()
+        o_raw_v = torch.empty(n, hd, device=dev) if kind == "prefill" else None
+        t_sv = _median_ms(lambda: K.delta_rule_scan(proj, pcols, aux, cu_d, kv_d, slots, vstate, nw, 1e-5, od, vH, vdd,
+                                                    err, col_blocks=4, o_raw=o_raw_v, tok_entry=ent), flush=flush)
+        b_pv = n * (3 * hd + vR) * 2 + n * 3 * hd * 4
+        b_sv = (n * (4 * hd * 2 + 3 * hd * 4 + hd * 2)) if kind == "prefill" else n_req * vH * vdd * vdd * 8
+        del proj, aux, vstate, od
+        # the gated delta rule: convolutions and unit vectors, then the recurrence, then head norm and gate
+        C = 2 * dG * dk + dH * dv
+        pc = C + dH * dv + 2 * dH
+        proj = rnd(n, pc)
+        rws, lanes = K.matrix_state_plan(dk)
+        conv_off = dH * rws * lanes * dv
+        state = torch.zeros(n_req, conv_off + (taps - 1) * C, device=dev)
+        conv_w, a_log, dtb = rnd(C, taps, dt=f32), rnd(dH, dt=f32), rnd(dH, dt=f32)
+        aux = torch.empty(n, C + 2 * dH, device=dev)
+        prep = lambda: K.conv_delta_prep(proj, pc, ctx, state, conv_off, conv_w, taps, a_log, dtb, aux, dH, dG, dk, dv,
+                                         1e-6, dk ** -0.5, err, bf)
+        t_p = _median_ms(prep, flush=flush)
+        prep()
+        o_raw = torch.empty(n, dH * dv, device=dev)
+        gd = dG * dk
+        t_s = _median_ms(lambda: K.matrix_state_scan(aux, (0, gd, 2 * gd, C, C + dH), False, True, dH // dG, ctx, state,
+                                                     o_raw, dH, dk, dv, err), flush=flush)
+        o = torch.empty(n, dH * dv, device=dev, dtype=bf)
+        nwm = rnd(dv, dt=f32)
+        t_n = _median_ms(lambda: K.head_norm_gate(o_raw, proj, pc, C, ent, nwm, 1e-5, o, dH, dv), flush=flush)
+        add(f"conv_delta_prep ({kind})", "delta_rule_prep", t_p, n * C * (2 + 4), 0, t_pv, b_pv, 0)
+        b_s = n * (C + 2 * dH + dH * dv) * 4 if kind == "prefill" else n_req * dH * dk * dv * 8
+        add(f"matrix_state_scan, delta rule ({kind})", "delta_rule_scan", t_s, b_s, 0, t_sv, b_sv, 0)
+        add(f"head_norm_gate ({kind})", "delta_rule_prep", t_n, n * dH * dv * (4 + 2 + 2), 0, t_pv, b_pv, 0)
+        del proj, state, aux, o_raw, o
+        # gated linear attention: the decay per key channel, then the same recurrence without correction
+        ghd, ghv = gH * gk_, gH * gv_
+        pc = 2 * ghd + 2 * ghv + rank
+        proj = rnd(n, pc)
+        a2t, bias = rnd(rank, ghd, dt=f32), rnd(ghd, dt=f32)
+        aux = torch.empty(n, 3 * ghd + ghv, device=dev)
+        rws, lanes = K.matrix_state_plan(gk_)
+        state = torch.zeros(n_req, gH * rws * lanes * gv_, device=dev)
+        prep = lambda: K.decay_gate_prep(proj, pc, ent, a2t, bias, 1.0 / rg["tau"], gk_ ** -0.5, aux, gH, gk_, gv_, bf)
+        t_p = _median_ms(prep, flush=flush)
+        prep()
+        o_raw = torch.empty(n, ghv, device=dev)
+        t_s = _median_ms(lambda: K.matrix_state_scan(aux, (0, ghd, 2 * ghd, 2 * ghd + ghv, 0), True, False, 1, ctx, state,
+                                                     o_raw, gH, gk_, gv_, err), flush=flush)
+        add(f"decay_gate_prep ({kind})", "delta_rule_prep", t_p, n * (2 * ghd + ghv + rank) * 2 + n * (3 * ghd + ghv) * 4,
+            0, t_pv, b_pv, 0)
+        b_s = n * (3 * ghd + 2 * ghv) * 4 if kind == "prefill" else n_req * gH * gk_ * gv_ * 8
+        add(f"matrix_state_scan, decay per channel ({kind})", "delta_rule_scan", t_s, b_s, 0, t_sv, b_sv, 0)
+        del proj, state, aux, o_raw
+        # attention whose heads exchange their weights, beside the like kernels with the sink
+        k_pool, v_pool = rnd(pages, G, ps, d), rnd(pages, G, ps, d)
+        qh, oh = rnd(n, H * d), torch.empty(n, H * d, device=dev, dtype=bf)
+        cross = torch.empty(n, H * G * d, device=dev)
+        talk = rnd(H, H, dt=f32)
+        t_x = _median_ms(lambda: K.head_talk_mix(cross, talk, ent, oh, H, G, d, d), flush=flush)
+        add(f"head_talk_mix ({kind})", None, t_x, n * H * d * (4 * G + 2), 0)
+        if kind == "prefill":
+            tiles = -(-T // 64)
+            t_m = _median_ms(lambda: K.paged_prefill_attention(qh, cross, k_pool, v_pool, cu_d, kv_d, table, ps, tiles, H, G,
+                                                               d, 0, d ** -0.5, err, cross=True), flush=flush)
+            t_v = _median_ms(lambda: K.paged_prefill_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, tiles, H, G,
+                                                               d, 0, d ** -0.5, err, sink=True), flush=flush)
+            pairs = T * T / 2
+            add("attention for every pair of heads, prompt (paged_prefill_attn, cross)", "paged_prefill_attn with the sink",
+                t_m, 0, pairs * H * G * 4 * d, t_v, 0, pairs * H * 4 * d)
+        else:
+            sp_v = K.decode_splits(n_req, G, 148, 64, max_keys=kv)
+            sp_m = max(1, min(32, (2 * 148) // max(1, n_req * G * G)))
+            po = torch.empty(n_req * H * G * max(sp_v, sp_m), d, device=dev)
+            pml = torch.empty(n_req * H * G * max(sp_v, sp_m), 2, device=dev)
+            t_m = _median_ms(lambda: K.paged_decode_attention(qh, cross, k_pool, v_pool, cu_d, kv_d, table, ps, H, G, d, 0,
+                                                              d ** -0.5, sp_m, po, pml, err, cross=True), flush=flush)
+            t_v = _median_ms(lambda: K.paged_decode_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, H, G, d, 0,
+                                                              d ** -0.5, sp_v, po, pml, err, sink=True), flush=flush)
+            kvb = n_req * kv * G * d * 2 * 2
+            add("attention for every pair of heads, decoded tokens (paged_decode_attn, cross)",
+                "paged_decode_attn with the sink", t_m, kvb, 0, t_v, kvb, 0)
+        del k_pool, v_pool, cross
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    return rows
+
+
+def mufevik_workload(args, pk):
+    """Prefill and decode throughput of Mufevik at the layer sizes of --sizes beside Vodelix (the
+    engine's closest model: a delta rule, experts with a shared one, attention on the warp-level
+    kernels) at the same width, layers and vocabulary, random weights, and the kernels of the two
+    side by side."""
+    import gc
+    import torch
+    hcfg = dict(MODEL)
+    hcfg.update(OTHER_SIZES.get(args.sizes, {}))
+    layers = args.layers or 12
+    hcfg["num_hidden_layers"] = layers
+    vcfg = vodelix_config(hcfg, layers)
+    vcfg.pop("loop", None)                       # every layer once, as in the other model
+    mcfg = mufevik_config(hcfg, layers)
+    page, pt = 64, args.prefill_tokens
+    out = {"workload": "mufevik", "sizes": args.sizes, "layers": layers, "batch": args.batch,
+           "context": args.context, "prefill_tokens": pt, "dtype": "bf16", "data": "synthetic", "models": {}}
+    for name, cfg in (("mufevik", mcfg), ("vodelix", vcfg)):
+        opts = dict(page_size=page, num_pages=(args.batch * (args.context + args.steps + args.warmup + 64) + pt) // page + 64,
+                    max_concurrent=max(64, args.batch), max_seq_len=max(args.context, pt) + 1024,
+                    max_batched_tokens=max(2048, pt), chunk_size=max(2048, pt))
+        model = build_model(cfg, opts)
+        pms = time_prefill(model, pt, cfg["vocab"], reps=3)
+        ids = fill_cache(model, args.batch, args.context)
+        dms, launches = time_decode(model, ids, args.steps, args.warmup, cfg["vocab"])
+        weights = sum(t.numel() * t.element_size() for t in _model_tensors(model))
+        out["models"][name] = {"prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(pt * 1000.0 / pms, 1),
+                               "decode_ms_per_step": round(dms, 4),
+                               "decode_tokens_per_s": round(args.batch * 1000.0 / dms, 1),
+                               "launches_per_decode_step": launches, "weight_bytes": weights,
+                               "layer_runs": len(model.runner.spec.schedule)}
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+    out["kernels"] = mufevik_kernel_table(mcfg, vcfg, hcfg, pk, pt, args.batch, args.context)
+    out["peaks"] = pk
+    return out
+
+
 def _model_tensors(model):
     seen, out = set(), []
     parts = [model.runner.model.embed, model.runner.model.final_norm, model.runner.model.head]
@@ -831,7 +1064,7 @@ def main():
                     help="layer sizes: Hunyuan 1.8B (the default, the headline configuration), 4B or 7B")
     ap.add_argument("--prefill-chunk", type=int, default=0,
                     help="with --only-prefill: also time the prompt in portions of this many tokens, a step each")
-    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax", "vodelix"],
+    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax", "vodelix", "mufevik"],
                     help="serve: a mix of requests through the scheduler; mixed-step: decoded tokens beside "
                          "one prompt portion in one step; radorax: prefill and decode of Radorax beside Hunyuan "
                          "Dense at equal layer sizes, and their kernels side by side; vodelix: the same for Vodelix; "
@@ -855,6 +1088,9 @@ def main():
         return 2
     args.warmup = max(args.warmup, 3)
 
+    if args.workload == "mufevik":
+        print(json.dumps(mufevik_workload(args, peaks())))
+        return
     if args.workload == "vodelix":
         print(json.dumps(vodelix_workload(args, peaks())))
         return 0

@@ -56,6 +56,9 @@ struct FusedArgs {
     int general;                    // 0: the defaults (whole head, contiguous halves, norm after, plain w)
     int sink;                       // (the plain form too) the softmax has one more candidate of score 0 that
                                     // has no value: exp2(0 - max) joins the sum where the output is divided
+    int cross;                      // (the plain form only) a CTA per (slice, pair of key/value heads, request):
+                                    // queries and keys of the first, values of the second; always through the
+                                    // scratch memory, and the merge kernel writes float [row][nq][nkv][d]
 };
 
 // A single element of the raw product (see raw2 for pairs).
@@ -266,7 +269,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     // kernel that produces q, k and v has finished.  Otherwise everything waits for that kernel.
     const bool early = FUSED && fa.has_kv != 0;
     if (!early) pdl_wait();
-    const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
+    const int split = blockIdx.x, e = blockIdx.z;
+    const int g = fa.cross ? blockIdx.y / nkv : blockIdx.y, gv = fa.cross ? blockIdx.y % nkv : g;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rep = nq / nkv;
     const int t = cu_q[e];
@@ -303,7 +307,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             const uint32_t st = wbase + s * 2 * TILE_BYTES;
             load_tile_async<D, TILE>(st, k_pool, table, num_pages, page_size, nkv, g, tj * TILE, lo,
                                      hi, lane, bad_page);
-            load_tile_async<D, TILE>(st + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+            load_tile_async<D, TILE>(st + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, gv,
                                      tj * TILE, lo, hi, lane, bad_page);
         }
         cp_async_commit();
@@ -353,7 +357,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             const uint32_t nk = wbase + ((it + NSTAGE - 1) % NSTAGE) * 2 * TILE_BYTES;
             load_tile_async<D, TILE>(nk, k_pool, table, num_pages, page_size, nkv, g, nxt * TILE, lo,
                                      hi, lane, bad_page);
-            load_tile_async<D, TILE>(nk + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+            load_tile_async<D, TILE>(nk + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, gv,
                                      nxt * TILE, lo, hi, lane, bad_page);
         }
         cp_async_commit();
@@ -496,11 +500,11 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             O += f * sm_o[(w * 16 + r) * D + c];
         }
         const int h = g * n_rep + r;
-        if (n_splits == 1) {
+        if (n_splits == 1 && !fa.cross) {
             if (fa.sink) L += exp2f(-mb);
             out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
         } else {
-            const long long pi = ((long long)e * nq + h) * n_splits + split;
+            const long long pi = (fa.cross ? ((long long)e * nq + h) * nkv + gv : (long long)e * nq + h) * n_splits + split;
             part_o[pi * D + c] = O;
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
@@ -583,7 +587,8 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
     pdl_launch_dependents();
     const bool early = FUSED && fa.has_kv != 0;
     if (!early) pdl_wait();
-    const int split = blockIdx.x, g = blockIdx.y, e = blockIdx.z;
+    const int split = blockIdx.x, e = blockIdx.z;
+    const int g = fa.cross ? blockIdx.y / nkv : blockIdx.y, gv = fa.cross ? blockIdx.y % nkv : g;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rep = nq / nkv;
     const int t = cu_q[e];
@@ -642,8 +647,9 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             if (lane == 0) mbar_expect_tx(bar, STAGE_BYTES);
             tma_tile_2d(st, &k_map, bar, 0, row);
             tma_tile_2d(st + HALF_TILE_BYTES, &k_map, bar, 64, row);
-            tma_tile_2d(st + TILE128_BYTES, &v_map, bar, 0, row);
-            tma_tile_2d(st + TILE128_BYTES + HALF_TILE_BYTES, &v_map, bar, 64, row);
+            const int row_v = row + (gv - g) * page_size;
+            tma_tile_2d(st + TILE128_BYTES, &v_map, bar, 0, row_v);
+            tma_tile_2d(st + TILE128_BYTES + HALF_TILE_BYTES, &v_map, bar, 64, row_v);
         }
     };
 #pragma unroll
@@ -960,14 +966,14 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
             O += f * sm_o[(w * 16 + r) * D + c];
         }
         const int h = g * n_rep + r;
-        if (n_splits == 1) {
+        if (n_splits == 1 && !fa.cross) {
             if (fa.sink) L += exp2f(-mb);
             out[((long long)t * nq + h) * D + c] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
         } else if (CLUSTER) {
             cl_o[r * D + c] = O;
             if (c == 0) { cl_ml[r * 2] = M; cl_ml[r * 2 + 1] = L; }
         } else {
-            const long long pi = ((long long)e * nq + h) * n_splits + split;
+            const long long pi = (fa.cross ? ((long long)e * nq + h) * nkv + gv : (long long)e * nq + h) * n_splits + split;
             part_o[pi * D + c] = O;
             if (c == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
@@ -1021,7 +1027,7 @@ paged_decode_attn_tma_kernel(const __grid_constant__ CUtensorMap k_map,
 template <int MAXS>
 __device__ __forceinline__ void merge_column(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                              __nv_bfloat16* __restrict__ out, long long base, int t, int nq,
-                                             int h, int d, int n_splits, int sink) {
+                                             int h, int d, int n_splits, int sink, int out_float) {
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float2 ml[MAXS];
         float o[MAXS];
@@ -1042,7 +1048,9 @@ __device__ __forceinline__ void merge_column(const float* __restrict__ part_o, c
             acc += f * o[s];
         }
         if (sink) L += exp2f(-mb);
-        out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        const float r = L > 0.f ? acc / L : 0.f;
+        if (out_float) ((float*)out)[((long long)t * nq + h) * d + c] = r;
+        else out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(r);
     }
 }
 
@@ -1054,7 +1062,7 @@ __device__ __forceinline__ void merge_column(const float* __restrict__ part_o, c
 // four loads in flight per thread.  Always in slice order.
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
-                                    int nq, int d, int n_splits, int sink) {
+                                    int nq, int d, int n_splits, int sink, int out_float) {
     __shared__ float wgt[64];
     __shared__ float m_s[64], l_s[64];
     pdl_launch_dependents();
@@ -1065,9 +1073,9 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     if (cu_q[e + 1] - t != 1) return;
     if (n_splits <= 64) {
         // all loads of a thread go out together; 16 slices' worth of registers when that is enough
-        if (n_splits <= 16) merge_column<16>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink);
-        else if (n_splits <= 32) merge_column<32>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink);
-        else merge_column<64>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink);
+        if (n_splits <= 16) merge_column<16>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink, out_float);
+        else if (n_splits <= 32) merge_column<32>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink, out_float);
+        else merge_column<64>(part_o, part_ml, out, base, t, nq, h, d, n_splits, sink, out_float);
         return;
     }
     for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
@@ -1103,7 +1111,9 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
             a3 += wgt[s + 3] * v3;
         }
         for (; s < n_splits; ++s) a0 += wgt[s] * po[(long long)s * d];
-        out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn((a0 + a1) + (a2 + a3));
+        const float r = (a0 + a1) + (a2 + a3);
+        if (out_float) ((float*)out)[((long long)t * nq + h) * d + c] = r;
+        else out[((long long)t * nq + h) * d + c] = __float2bfloat16_rn(r);
     }
 }
 
@@ -1212,31 +1222,33 @@ int launch_decode(const void* q, void* out, float* part_o, float* part_ml, const
             return (int)cudaGetLastError();
         configured = true;
     }
-    dim3 grid(n_splits, nkv, n_entries);
+    const int cross = (!FUSED && fa.cross) ? 1 : 0;
+    const int nq_out = cross ? nq * nkv : nq;       // heads of the merged output
+    dim3 grid(n_splits, cross ? nkv * nkv : nkv, n_entries);
     // pages of whole tiles, or tiles of whole pages (8 or 16 tokens: a piece of a tile is then a multiple
     // of the 1024 bytes the swizzle pattern repeats after)
     const bool pages_fit = page_size % TILE == 0 || (page_size >= 8 && TILE % page_size == 0);
     if (D == D128 && pages_fit && tma_path_enabled()) {
         // 2 to 8 slices merge themselves in a cluster; more go through scratch memory and a second kernel
-        const bool cluster = n_splits > 1 && n_splits <= 8 && cluster_merge_enabled();
+        const bool cluster = n_splits > 1 && n_splits <= 8 && !cross && cluster_merge_enabled();
         const int rc = launch_decode_tma<FUSED, GENERAL>(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
                                                 block_table, max_blocks, num_pages, page_size, nq, nkv,
                                                 window, scale, n_splits, err, fa, grid, cluster, st);
         if (rc != 0) return rc;
-        if (n_splits > 1 && !cluster)
-            return crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
-                                (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq,
-                                D, n_splits, fa.sink);
+        if ((n_splits > 1 && !cluster) || cross)
+            return crane_launch(decode_merge_kernel, dim3(n_entries, nq_out), dim3(D >= 128 ? 128 : 64), 0, st,
+                                (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq_out,
+                                D, n_splits, fa.sink, cross);
         return 0;
     }
     int rc = crane_launch(kern, grid, dim3(WARPS * 32), smem, st, (const __nv_bfloat16*)q,
                           (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, cu_q, kv_len, block_table, max_blocks, num_pages,
                           page_size, nq, nkv, window, scale * 1.4426950408889634f, n_splits, err, fa);
-    if (rc == 0 && n_splits > 1)
-        rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq), dim3(D >= 128 ? 128 : 64), 0, st,
-                          (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq, D,
-                          n_splits, fa.sink);
+    if (rc == 0 && (n_splits > 1 || cross))
+        rc = crane_launch(decode_merge_kernel, dim3(n_entries, nq_out), dim3(D >= 128 ? 128 : 64), 0, st,
+                          (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q, nq_out, D,
+                          n_splits, fa.sink, cross);
     return rc;
 }
 }  // namespace
@@ -1300,18 +1312,22 @@ CRANE_API int crane_paged_decode_attention_supports(int d, int nq, int nkv) {
 // more or no rows are skipped, so that a step's prompt portions can go to the
 // prefill kernel and its decoded tokens here.  part_o needs
 // n_entries * nq * n_splits * d floats and part_ml n_entries * nq * n_splits * 2
-// when n_splits > 1.
+// when n_splits > 1.  cross != 0: `out` is float [rows][nq][nkv][d], every query head's weights
+// applied to the values of every key/value head; the scratch memory is always used and takes nkv
+// times as much.
 CRANE_API int crane_paged_decode_attention(const void* q, void* out, float* part_o, float* part_ml,
                                            const void* k_pool, const void* v_pool, const int* cu_q,
                                            const int* kv_len, const int* block_table, int max_blocks,
                                            int num_pages, int page_size, int n_entries, int nq, int nkv,
                                            int d, int window, float scale, int n_splits, int sink,
-                                           int* err, cudaStream_t st) {
+                                           int cross, int* err, cudaStream_t st) {
     if (n_entries <= 0) return 0;
-    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64)
+    if (!crane_paged_decode_attention_supports(d, nq, nkv) || n_splits < 1 || n_splits > 64 ||
+        (cross && (part_o == nullptr || part_ml == nullptr)))
         return (int)cudaErrorInvalidValue;
     FusedArgs none = {};
     none.sink = sink;
+    none.cross = cross ? 1 : 0;
     return launch_for_head_size(d, 0, q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, block_table,
                                 max_blocks, num_pages, page_size, n_entries, nq, nkv, window, scale,
                                 n_splits, err, &none, st);
@@ -1415,6 +1431,6 @@ CRANE_API int crane_paged_decode_attention_noalloc(const void* q, void* out, con
     }
     return crane_paged_decode_attention(q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len,
                                         block_table, max_blocks, num_pages, page_size, n_entries, nq,
-                                        nkv, d, window, scale, n_splits, 0, err, stream);
+                                        nkv, d, window, scale, n_splits, 0, 0, err, stream);
 }
 #endif  // CRANE_HEAD_SIZE

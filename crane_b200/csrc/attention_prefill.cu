@@ -28,7 +28,8 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
                           const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_q,
                           const int* __restrict__ kv_len, const int* __restrict__ block_table,
                           int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv,
-                          int window, float scale_log2, int skip_single, int sink, int* err) {
+                          int window, float scale_log2, int skip_single, int sink,
+                          float* __restrict__ out_cross, int* err) {
     constexpr int RB = Tile<D>::ROW_BYTES;
     constexpr int TILE_BYTES = BKV * RB;
     constexpr int KS = D / 16, DN = D / 8;
@@ -49,7 +50,10 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
         tile -= tiles;
     }
     if (e >= n_entries) return;
-    const int h = blockIdx.x, g = h / (nq / nkv);
+    // `out_cross`: a CTA per (query head, key/value head): the head's own keys and scores, the values
+    // of key/value head gv, the result in float at [row][head][gv][D] (for heads that exchange their weights)
+    const int h = out_cross != nullptr ? blockIdx.x / nkv : blockIdx.x, g = h / (nq / nkv);
+    const int gv = out_cross != nullptr ? blockIdx.x % nkv : g;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = cu_q[e], q_len = cu_q[e + 1] - row0;
     const int pos0 = kv_len[e] - q_len;                  // position of the request's first row
@@ -87,7 +91,7 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
     const uint32_t sbase = smem_u32(smem);
     load_tile_async<D, BKV, THREADS>(sbase, k_pool, table, num_pages, page_size, nkv, g, t_begin * BKV,
                                      lo, p_last, threadIdx.x, bad_page);
-    load_tile_async<D, BKV, THREADS>(sbase + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, g,
+    load_tile_async<D, BKV, THREADS>(sbase + TILE_BYTES, v_pool, table, num_pages, page_size, nkv, gv,
                                      t_begin * BKV, lo, p_last, threadIdx.x, bad_page);
     cp_async_commit();
     for (int ti = t_begin, it = 0; ti < t_end; ++ti, ++it) {
@@ -97,7 +101,7 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
             load_tile_async<D, BKV, THREADS>(nk, k_pool, table, num_pages, page_size, nkv, g,
                                              (ti + 1) * BKV, lo, p_last, threadIdx.x, bad_page);
             load_tile_async<D, BKV, THREADS>(nk + TILE_BYTES, v_pool, table, num_pages, page_size, nkv,
-                                             g, (ti + 1) * BKV, lo, p_last, threadIdx.x, bad_page);
+                                             gv, (ti + 1) * BKV, lo, p_last, threadIdx.x, bad_page);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -192,6 +196,19 @@ paged_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __
     }
     const float inv_a = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_b = l[1] > 0.f ? 1.f / l[1] : 0.f;
     const int c0 = (lane & 3) * 2;
+    if (out_cross != nullptr) {
+        const long long pairs = (long long)nq * nkv;
+#pragma unroll
+        for (int dn = 0; dn < DN; ++dn) {
+            if (ra < r_end)
+                *(float2*)(out_cross + ((long long)(row0 + ra) * pairs + blockIdx.x) * D + dn * 8 + c0) =
+                    make_float2(o[dn][0] * inv_a, o[dn][1] * inv_a);
+            if (rb < r_end)
+                *(float2*)(out_cross + ((long long)(row0 + rb) * pairs + blockIdx.x) * D + dn * 8 + c0) =
+                    make_float2(o[dn][2] * inv_b, o[dn][3] * inv_b);
+        }
+        return;
+    }
 #pragma unroll
     for (int dn = 0; dn < DN; ++dn) {
         if (ra < r_end)
@@ -207,7 +224,7 @@ template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* cu_q,
                    const int* kv_len, const int* block_table, int max_blocks, int num_pages,
                    int page_size, int n_entries, int total_q_tiles, int nq, int nkv, int window,
-                   float scale, int skip_single, int sink, int* err, cudaStream_t st) {
+                   float scale, int skip_single, int sink, float* out_cross, int* err, cudaStream_t st) {
     constexpr int smem = 4 * BKV * Tile<D>::ROW_BYTES;
     auto kern = paged_prefill_attn_kernel<D>;
     static bool configured = false;
@@ -216,11 +233,12 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
             return (int)cudaGetLastError();
         configured = true;
     }
-    dim3 grid(nq, total_q_tiles);
+    dim3 grid(out_cross != nullptr ? nq * nkv : nq, total_q_tiles);
     kern<<<grid, THREADS, smem, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
                                       kv_len, block_table, max_blocks, num_pages, page_size, n_entries,
-                                      nq, nkv, window, scale * 1.4426950408889634f, skip_single, sink, err);
+                                      nq, nkv, window, scale * 1.4426950408889634f, skip_single, sink,
+                                      out_cross, err);
     return crane_launch_status();
 }
 }  // namespace
@@ -232,13 +250,13 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
 #define CRANE_PREFILL_LAUNCHER_ARGS                                                                    \
     const void *q, void *out, const void *k_pool, const void *v_pool, const int *cu_q, const int *kv_len, \
         const int *block_table, int max_blocks, int num_pages, int page_size, int n_entries,            \
-        int total_q_tiles, int nq, int nkv, int window, float scale, int skip_single, int sink, int *err, \
-        cudaStream_t st
+        int total_q_tiles, int nq, int nkv, int window, float scale, int skip_single, int sink,         \
+        float *out_cross, int *err, cudaStream_t st
 #ifdef CRANE_HEAD_SIZE
 extern "C" int CRANE_CAT(crane_prefill_launch_d, CRANE_HEAD_SIZE)(CRANE_PREFILL_LAUNCHER_ARGS) {
     return launch_prefill<CRANE_HEAD_SIZE>(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks,
                                            num_pages, page_size, n_entries, total_q_tiles, nq, nkv, window,
-                                           scale, skip_single, sink, err, st);
+                                           scale, skip_single, sink, out_cross, err, st);
 }
 #else
 #ifdef CRANE_HEAD_SIZE_LIST          // the head sizes linked into this library (see attention_decode.cu)
@@ -260,20 +278,22 @@ CRANE_API int crane_paged_prefill_attention_supports(int d, int nq, int nkv) {
 
 // total_q_tiles: sum over the entries of ceil(q_len / 64) (an upper bound will do: tiles beyond
 // the real ones do nothing).  skip_single != 0: entries of exactly one token are left out (they
-// count no tile either); their rows of `out` are for the decode kernel to write.
+// count no tile either); their rows of `out` are for the decode kernel to write.  out_cross
+// (float [rows][nq][nkv][d], or null): every query head's weights applied to the values of every
+// key/value head, written there instead of `out`.
 CRANE_API int crane_paged_prefill_attention(const void* q, void* out, const void* k_pool,
                                             const void* v_pool, const int* cu_q, const int* kv_len,
                                             const int* block_table, int max_blocks, int num_pages,
                                             int page_size, int n_entries, int total_q_tiles, int nq,
                                             int nkv, int d, int window, float scale, int skip_single,
-                                            int sink, int* err, cudaStream_t st) {
+                                            int sink, float* out_cross, int* err, cudaStream_t st) {
     if (n_entries <= 0 || total_q_tiles <= 0) return 0;
     if (!crane_paged_prefill_attention_supports(d, nq, nkv)) return (int)cudaErrorInvalidValue;
 #define CASE(DD)                                                                                      \
     case DD:                                                                                          \
         return crane_prefill_launch_d##DD(q, out, k_pool, v_pool, cu_q, kv_len, block_table, max_blocks, \
                                           num_pages, page_size, n_entries, total_q_tiles, nq, nkv,      \
-                                          window, scale, skip_single, sink, err, st);
+                                          window, scale, skip_single, sink, out_cross, err, st);
     switch (d) { CRANE_PREFILL_HEAD_SIZES(CASE) }
 #undef CASE
     return (int)cudaErrorInvalidValue;

@@ -283,8 +283,8 @@ head_talk_mix_kernel(const float* __restrict__ cross, const float* __restrict__ 
     const int t = blockIdx.x;
     if (tok_entry[t] < 0) return;
     const int rep = H / G;
-    for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
-        const int h = idx / dv, c = idx % dv;
+    for (int idx = threadIdx.x; idx < H * out_head; idx += blockDim.x) {     // out_head <= dv columns are kept
+        const int h = idx / out_head, c = idx % out_head;
         const float* src = cross + ((long long)t * H * G + h / rep) * dv + c;
         float acc = 0.f;
         for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], src[(long long)g * G * dv], acc);
@@ -403,7 +403,7 @@ CRANE_API int crane_head_norm_gate(int dtype, const float* o_raw, const void* pr
 CRANE_API int crane_head_talk_mix(int dtype, const float* cross, const float* talk, const int* tok_entry, void* out,
                                   int n_tokens, int H, int G, int dv, int out_head, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (G <= 0 || H % G) return (int)cudaErrorInvalidValue;
+    if (G <= 0 || H % G || out_head > dv) return (int)cudaErrorInvalidValue;
     DISPATCH_T(dtype, return crane_launch(head_talk_mix_kernel<T>, dim3(n_tokens), dim3(256), 0, st, cross, talk,
                                           tok_entry, (T*)out, H, G, dv, out_head));
 }

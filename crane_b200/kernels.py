@@ -30,9 +30,9 @@ _SIGNATURES = {
     "crane_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
     "crane_paged_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P, P],
     "crane_paged_decode_attention_supports": [I, I, I],
-    "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    "crane_paged_decode_attention": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
     "crane_paged_prefill_attention_supports": [I, I, I],
-    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    "crane_paged_prefill_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "crane_paged_decode_attention_fused": [P, P, I, L, I, I, I, P, P, I, P, P, F, P, P, P, P, P, P, P, P,
                                            I, I, I, I, I, I, I, I, F, I, I, I, I, F, P, P],
     "crane_prefill_attention_tc_supports": [I, I, I, I],
@@ -745,18 +745,23 @@ class Kernels:
         return bool(self.lib.crane_paged_decode_attention_supports(d, nq, nkv))
 
     def paged_decode_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
-                               nq, nkv, d, window, scale, n_splits, part_o, part_ml, err, sink: bool = False) -> None:
+                               nq, nkv, d, window, scale, n_splits, part_o, part_ml, err, sink: bool = False,
+                               cross: bool = False) -> None:
         """The entries of exactly one token (bfloat16); entries with more or no
         rows are skipped.  ``part_o`` [entries * nq * n_splits * d] and ``part_ml``
         [entries * nq * n_splits * 2] floats are scratch for n_splits > 1.  ``sink``: the
-        softmax has one more candidate of score 0 that has no value."""
+        softmax has one more candidate of score 0 that has no value.  ``cross``: ``out`` is float
+        [n, nq, nkv, d], every query head's weights applied to the values of EVERY key/value head
+        (for heads that exchange their weights); the scratch is always used and nkv times as large."""
+        assert not cross or (out.dtype == torch.float32 and part_o is not None)
         n_entries = kv_len.shape[0]
         self.require_head_size(d)
         self._check(self.lib.crane_paged_decode_attention(
             q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml), k_pool.data_ptr(),
             v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], k_pool.shape[0], page_size, n_entries, nq, nkv, d, int(window),
-            float(scale), int(n_splits), 1 if sink else 0, err.data_ptr(), self._stream(q)), "paged_decode_attention")
+            float(scale), int(n_splits), 1 if sink else 0, 1 if cross else 0, err.data_ptr(), self._stream(q)),
+            "paged_decode_attention")
 
     def prefill_attention_supports(self, d: int, nq: int, nkv: int) -> bool:
         self.require_head_size(d)
@@ -764,17 +769,19 @@ class Kernels:
 
     def paged_prefill_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, block_table, page_size,
                                 total_q_tiles, nq, nkv, d, window, scale, err, skip_single=False,
-                                sink: bool = False) -> None:
+                                sink: bool = False, cross: bool = False) -> None:
         """Any mix of portions and single tokens (bfloat16).  ``total_q_tiles``:
         the sum over the entries of ceil(tokens / 64), or more.  ``skip_single``:
-        entries of exactly one token are left to the decode kernel.  ``sink`` as in
+        entries of exactly one token are left to the decode kernel.  ``sink`` and ``cross`` as in
         ``paged_decode_attention``."""
+        assert not cross or out.dtype == torch.float32
         self.require_head_size(d)
         self._check(self.lib.crane_paged_prefill_attention(
             q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(),
             kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0],
             page_size, kv_len.shape[0], int(total_q_tiles), nq, nkv, d, int(window), float(scale),
-            1 if skip_single else 0, 1 if sink else 0, err.data_ptr(), self._stream(q)), "paged_prefill_attention")
+            1 if skip_single else 0, 1 if sink else 0, out.data_ptr() if cross else None, err.data_ptr(),
+            self._stream(q)), "paged_prefill_attention")
 
     def prefill_attention_tc_supports(self, d: int, nq: int, nkv: int, page_size: int) -> bool:
         return bool(self.lib.crane_prefill_attention_tc_supports(d, nq, nkv, page_size))

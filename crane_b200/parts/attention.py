@@ -243,6 +243,8 @@ class SinkAttention(Part):
         # attention kernels are compiled for (zero-filled columns add nothing to a score, and the
         # value columns beyond vdim are never read back); the 32-bit path stores them as wide as they are.
         self.store = int(a.get("head_dim") or 0) if not rt.exact else 0
+        if os.environ.get("CRANE_TALKING_ATTENTION", "mma") == "simt":       # the FP32-core kernel in bfloat16 too
+            self.store = 0
         if self.store and not (rt.kernels.prefill_attention_supports(self.store, self.H, self.G)
                                and rt.kernels.decode_attention_supports(self.store, self.H, self.G)):
             self.store = 0
@@ -294,29 +296,31 @@ def sink_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, scal
                            cross: bool = False) -> int:
     """Attention of q [n, H, D] over pools of head size D with the warp-level kernels: entries of
     one token through the split-KV decode kernel where that pays, the others through the prefill
-    kernel.  Returns the launches."""
+    kernel.  ``cross``: ``o`` is float [n, H, G, D], every query head's weights applied to the values
+    of every key/value head (a CTA per pair of key/value heads where there was one per head).
+    Returns the launches."""
     n = q.shape[0]
     decode = ctx.max_q_len == 1 and n == ctx.n_entries
     singles = 0 if decode else getattr(ctx, "single_entries", 0)
     launches = 0
     if decode or singles:
         if decode:
-            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * G)))
+            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * G * (G if cross else 1))))
         else:
-            splits = min(8, k.decode_splits(singles, G, rt.num_sms, max_splits))
+            splits = min(8, k.decode_splits(singles, G * (G if cross else 1), rt.num_sms, max_splits))
         part_o = part_ml = None
-        if splits > 1:
-            rows = rt.max_decode_rows * H * 32
+        if splits > 1 or cross:
+            rows = rt.max_decode_rows * H * (G if cross else 1) * 32
             part_o = rt.ws.get("attn_part_o", rows, D, torch.float32, cap=rows)
             part_ml = rt.ws.get("attn_part_ml", rows, 2, torch.float32, cap=rows)
         k.paged_decode_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size, H, G, D,
-                                 window, scale, splits, part_o, part_ml, rt.err, sink=sink)
-        launches += 2 if splits > 1 else 1
+                                 window, scale, splits, part_o, part_ml, rt.err, sink=sink, cross=cross)
+        launches += 2 if splits > 1 or cross else 1
         if decode:
             return launches
     tiles = query_tiles(ctx, 64, skip_single=bool(singles))
     k.paged_prefill_attention(q, o, cache.k, cache.v, ctx.cu_q, ctx.kv_len, table, cache.page_size, tiles, H, G, D,
-                              window, scale, rt.err, skip_single=bool(singles), sink=sink)
+                              window, scale, rt.err, skip_single=bool(singles), sink=sink, cross=cross)
     return launches + 1
 
 
@@ -372,8 +376,10 @@ class TalkingAttention(Part):
         # bfloat16: keys and values at one common head size that the warp-level kernels are compiled for
         # (zero-filled columns add nothing to a score; value columns beyond vdim are never read back)
         self.store = int(a.get("head_dim") or 0) if not rt.exact else 0
-        if self.store and not (rt.kernels.prefill_attention_supports(self.store, self.H * self.G, self.G)
-                               and getattr(rt.kernels, "mma_attention_takes_cross", False)):
+        if os.environ.get("CRANE_TALKING_ATTENTION", "mma") == "simt":       # the FP32-core kernel in bfloat16 too
+            self.store = 0
+        if self.store and not (rt.kernels.prefill_attention_supports(self.store, self.H, self.G)
+                               and rt.kernels.decode_attention_supports(self.store, self.H, self.G)):
             self.store = 0
         self.max_splits = int(os.environ.get("CRANE_DECODE_SPLITS", "64"))
 
