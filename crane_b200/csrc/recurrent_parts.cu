@@ -29,7 +29,9 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // ------------------------------------------------------ convolution + delta-rule inputs
 // proj row: [q (G d) | k (G d) | v (H dv) | gate (H dv) | b (H) | a (H)].  aux row: [q (G d) | k (G d) |
 // v (H dv) | w (H) | beta (H)].  conv_w [2 G d + H dv][taps] float.  conv_state: inside the slot's state
-// at `conv_off`, [taps - 1][C].  One CTA per token.
+// at `conv_off`, [taps - 1][C].  Grid (tokens, blocks of heads); a warp per head of q, k or v (2 G + H of
+// them): a q or k head is written as the convolution left it, then scaled by the same lanes once its
+// sum of squares is known.
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_delta_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_entry,
@@ -39,7 +41,6 @@ conv_delta_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_en
                        const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                        float* __restrict__ aux, int aux_cols, int H, int G, int d, int dv, float key_eps,
                        float q_scale, int* err) {
-    extern __shared__ float vals[];                   // [C]
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -51,37 +52,44 @@ conv_delta_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_en
     const int start = kv_len[e] - (cu_q[e + 1] - first);             // tokens of the request before the step
     const int slot = slots[e];
     if (slot < 0 || slot >= n_slots) {
-        if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
         return;
     }
     const float* cs = state + (long long)slot * slot_stride + conv_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int back = taps - 1 - j;
-            float x = 0.f;
-            if (i - back >= 0) x = proj.load((long long)(t - back) * cols + c);
-            else if (start + i - back >= 0) x = cs[(long long)(taps - 1 + i - back) * C + c];
-            acc = fmaf(conv_w[(long long)c * taps + j], x, acc);
-        }
-        vals[c] = silu_f(acc);
-    }
-    __syncthreads();
     float* out = aux + (long long)t * aux_cols;
-    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int hd = wib; hd < 2 * G; hd += nw) {                        // q heads, then k heads
+    const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int unit = blockIdx.y * nw + (threadIdx.x >> 5); unit < 2 * G + H; unit += gridDim.y * nw) {
+        const bool qk = unit < 2 * G;
+        const int width = qk ? d : dv;
+        const int c_first = qk ? unit * d : 2 * G * d + (unit - 2 * G) * dv;
         float ss = 0.f;
-        for (int c = lane; c < d; c += 32) { const float v = vals[hd * d + c]; ss = fmaf(v, v, ss); }
-        ss = warp_sum(ss);
-        const float r = rsqrtf(ss + key_eps) * (hd < G ? q_scale : 1.f);
-        for (int c = lane; c < d; c += 32) out[hd * d + c] = vals[hd * d + c] * r;
+        for (int cc = lane; cc < width; cc += 32) {
+            const int c = c_first + cc;
+            float acc = 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j;
+                float x = 0.f;
+                if (i - back >= 0) x = proj.load((long long)(t - back) * cols + c);
+                else if (start + i - back >= 0) x = cs[(long long)(taps - 1 + i - back) * C + c];
+                acc = fmaf(conv_w[(long long)c * taps + j], x, acc);
+            }
+            const float v = silu_f(acc);
+            out[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (qk) {
+            ss = warp_sum(ss);
+            const float r = rsqrtf(ss + key_eps) * (unit < G ? q_scale : 1.f);
+            for (int cc = lane; cc < width; cc += 32) out[c_first + cc] *= r;      // each lane its own elements
+        }
     }
-    for (int c = threadIdx.x; c < H * dv; c += blockDim.x) out[2 * G * d + c] = vals[2 * G * d + c];
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        const long long row = (long long)t * cols + C + H * dv;
-        const float b = proj.load(row + h), a = proj.load(row + H + h);
-        out[C + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
-        out[C + H + h] = 1.f / (1.f + expf(-b));
+    if (blockIdx.y == 0) {
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const long long row = (long long)t * cols + C + H * dv;
+            const float b = proj.load(row + h), a = proj.load(row + H + h);
+            out[C + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+            out[C + H + h] = 1.f / (1.f + expf(-b));
+        }
     }
 }
 
@@ -141,30 +149,44 @@ decay_gate_prep_kernel(GemmOut<T> proj, int cols, const int* __restrict__ tok_en
     for (int r = threadIdx.x; r < rank; r += blockDim.x) low[r] = proj.load(row + 2 * hd + 2 * hv + r);
     __syncthreads();
     float* out = aux + (long long)t * aux_cols;
-    for (int c = threadIdx.x; c < hd; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hd; c += gridDim.y * blockDim.x) {
         out[c] = proj.load(row + c) * q_scale;
         out[hd + c] = proj.load(row + hd + c);
         float z = bias[c];
+#pragma unroll 8
         for (int r = 0; r < rank; ++r) z = fmaf(low[r], a2t[(long long)r * hd + c], z);
         // sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau)
         out[2 * hd + hv + c] = expf(-softplus_f(-z) * inv_tau);
     }
-    for (int c = threadIdx.x; c < hv; c += blockDim.x) out[2 * hd + c] = proj.load(row + 2 * hd + c);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hv; c += gridDim.y * blockDim.x)
+        out[2 * hd + c] = proj.load(row + 2 * hd + c);
 }
 
 // ------------------------------------------------------ the recurrence
 // grid (entries, heads, column blocks); block = COLS columns x LANES lanes.  aux offsets: q_off, k_off,
 // v_off, w_off, beta_off (beta only with `delta`); q/k head of head h is h / qk_rep; w is [Hqk d]
 // (w_vec) or [H].  o_raw float [n][H dv].
-constexpr int SCAN_TOKENS = 8;
-template <int ROWS>
+// Tokens come in tiles of `tile_tokens` whose vectors all threads copy into shared memory with 4-byte
+// asynchronous copies, the next tile while the current one is walked: a tile's fetch from DRAM is as
+// long as walking several tokens, and the walk must not wait for it.
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+constexpr int SCAN_TOKENS = 16;
+// FULL: the lanes' rows are exactly the dk rows, and no row is tested.
+template <int ROWS, bool FULL>
 __global__ void __launch_bounds__(256)
 matrix_state_scan_kernel(const float* __restrict__ aux, int aux_cols, int q_off, int k_off, int v_off, int w_off,
                          int beta_off, int w_vec, int delta, int qk_rep, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_len, const int* __restrict__ slots, int n_slots,
                          float* __restrict__ state, long long slot_stride, float* __restrict__ o_raw,
-                         int H, int dk, int dv, int lanes, int cols_per_block, int* err) {
-    extern __shared__ float tile[];                   // [SCAN_TOKENS][3 dk + cols + 2]
+                         int H, int dk, int dv, int lanes, int cols_per_block, int tile_tokens, int vec4, int* err) {
+    extern __shared__ __align__(16) float tile[];     // two tiles of [tile_tokens][3 dk + cols + 2, to a multiple of 4]
     pdl_launch_dependents();
     pdl_wait();
     const int e = blockIdx.x, h = blockIdx.y;
@@ -179,44 +201,62 @@ matrix_state_scan_kernel(const float* __restrict__ aux, int aux_cols, int q_off,
     const int lane = threadIdx.x % lanes, cl = threadIdx.x / lanes;
     const int col = blockIdx.z * cols_per_block + cl;
     const bool live = cl < cols_per_block && col < dv;
+    const int hq = h / qk_rep;
+    const int stride = (3 * dk + cols_per_block + 2 + 3) & ~3;       // rows start on 16 bytes
+    const int c0 = blockIdx.z * cols_per_block;
+    const int wib = threadIdx.x >> 5, wl = threadIdx.x & 31, nw = blockDim.x >> 5;
+    // a warp per token; each of a token's vectors is one run of the row, copied 16 bytes a lane (`vec4`: every
+    // run starts on 16 bytes and is a multiple of them) or 4
+    auto run = [&](float* dst, const float* src, int n) {
+        if (vec4) for (int j = wl * 4; j < n; j += 128) cp_async16(dst + j, src + j);
+        else for (int j = wl; j < n; j += 32) cp_async4(dst + j, src + j);
+    };
+    auto fetch = [&](int t0, float* buf) {
+        const int nt = min(tile_tokens, q_len - t0);
+        for (int tt = wib; tt < nt; tt += nw) {
+            const float* a = aux + (long long)(first + t0 + tt) * aux_cols;
+            float* b = buf + tt * stride;
+            run(b, a + q_off + hq * dk, dk);
+            run(b + dk, a + k_off + hq * dk, dk);
+            if (w_vec) run(b + 2 * dk, a + w_off + hq * dk, dk);
+            const int nv = min(cols_per_block, dv - c0);
+            run(b + 3 * dk, a + v_off + h * dv + c0, nv);
+            if (wl == 0) {
+                if (w_vec) b[3 * dk + cols_per_block] = 1.f;
+                else cp_async4(b + 3 * dk + cols_per_block, a + w_off + h);
+            } else if (wl == 1) {
+                if (delta) cp_async4(b + 3 * dk + cols_per_block + 1, a + beta_off + h);
+                else b[3 * dk + cols_per_block + 1] = 1.f;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, tile);
     // state [H][ROWS][dv][lanes]
     float* sp = state + (long long)slot * slot_stride + (long long)h * ROWS * dv * lanes;
     float s[ROWS];
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
         s[i] = (live && start > 0) ? sp[((long long)i * dv + col) * lanes + lane] : 0.f;
-    const int hq = h / qk_rep;
-    const int stride = 3 * dk + cols_per_block + 2;
-    const int c0 = blockIdx.z * cols_per_block;
-    for (int t0 = 0; t0 < q_len; t0 += SCAN_TOKENS) {
-        const int nt = min(SCAN_TOKENS, q_len - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * stride; idx += blockDim.x) {
-            const int tt = idx / stride, j = idx % stride;
-            const float* a = aux + (long long)(first + t0 + tt) * aux_cols;
-            float v;
-            if (j < dk) v = a[q_off + hq * dk + j];
-            else if (j < 2 * dk) v = a[k_off + hq * dk + j - dk];
-            else if (j < 3 * dk) v = w_vec ? a[w_off + hq * dk + j - 2 * dk] : 0.f;
-            else if (j < 3 * dk + cols_per_block) {
-                const int c = c0 + j - 3 * dk;
-                v = c < dv ? a[v_off + h * dv + c] : 0.f;
-            } else if (j == 3 * dk + cols_per_block) v = w_vec ? 1.f : a[w_off + h];
-            else v = delta ? a[beta_off + h] : 1.f;
-            tile[idx] = v;
-        }
-        __syncthreads();
+    const int tile_floats = tile_tokens * stride;
+    for (int t0 = 0, it = 0; t0 < q_len; t0 += tile_tokens, ++it) {
+        const int nt = min(tile_tokens, q_len - t0);
+        const float* cur = tile + (it & 1) * tile_floats;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();              // the tile is there for all; all have left the other one
+        if (t0 + tile_tokens < q_len) fetch(t0 + tile_tokens, tile + ((it + 1) & 1) * tile_floats);
+#pragma unroll(ROWS == 8 ? 2 : 1)
         for (int tt = 0; tt < nt; ++tt) {
-            const float* q = tile + tt * stride;
+            const float* q = cur + tt * stride;
             const float* k = q + dk;
             const float* w = k + dk;
-            const float vv = cl < cols_per_block ? q[3 * dk + cl] : 0.f;
+            const float vv = live ? q[3 * dk + cl] : 0.f;
             const float ws = q[3 * dk + cols_per_block], beta = q[3 * dk + cols_per_block + 1];
             float dot = 0.f;
 #pragma unroll
             for (int i = 0; i < ROWS; ++i) {
                 const int r = lane + i * lanes;
-                if (r < dk) {
+                if (FULL || r < dk) {
                     s[i] *= w_vec ? w[r] : ws;
                     dot = fmaf(s[i], k[r], dot);
                 }
@@ -230,7 +270,7 @@ matrix_state_scan_kernel(const float* __restrict__ aux, int aux_cols, int q_off,
 #pragma unroll
             for (int i = 0; i < ROWS; ++i) {
                 const int r = lane + i * lanes;
-                if (r < dk) {
+                if (FULL || r < dk) {
                     s[i] = fmaf(k[r], u, s[i]);
                     rd = fmaf(s[i], q[r], rd);
                 }
@@ -273,18 +313,17 @@ head_norm_gate_kernel(const float* __restrict__ o_raw, GemmOut<T> proj, int cols
 
 // ------------------------------------------------------ heads that exchange their weights
 // cross [n][H][G][dv] float: query head g's softmax weights applied to the values of every key/value
-// head.  out[t][h] = sum_g talk[h][g] cross[t][g][h / (H / G)].
+// head.  out[t][h] = sum_g talk[h][g] cross[t][g][h / (H / G)].  Grid (tokens, heads).
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 head_talk_mix_kernel(const float* __restrict__ cross, const float* __restrict__ talk,
                      const int* __restrict__ tok_entry, T* __restrict__ out, int H, int G, int dv, int out_head) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, h = blockIdx.y;
     if (tok_entry[t] < 0) return;
     const int rep = H / G;
-    for (int idx = threadIdx.x; idx < H * out_head; idx += blockDim.x) {     // out_head <= dv columns are kept
-        const int h = idx / out_head, c = idx % out_head;
+    for (int c = threadIdx.x; c < out_head; c += blockDim.x) {               // out_head <= dv columns are kept
         const float* src = cross + ((long long)t * H * G + h / rep) * dv + c;
         float acc = 0.f;
         for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], src[(long long)g * G * dv], acc);
@@ -329,13 +368,14 @@ CRANE_API int crane_conv_delta_prep(int dtype, const void* proj, const float* pr
                                     float q_scale, int* err, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     const int C = 2 * G * d + H * dv;
-    if (taps < 1 || taps > MAX_TAPS || (size_t)C * 4 > 160 * 1024) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)C * sizeof(float);
+    if (taps < 1 || taps > MAX_TAPS) return (int)cudaErrorInvalidValue;
+    // a warp per head; with few tokens the heads spread over more CTAs
+    const int units = 2 * G + H;
+    int by = (units + 7) / 8;
+    while (by > 1 && (long long)n_tokens * by > 4 * 148) by = (by + 1) / 2;
     DISPATCH_T(dtype, {
         GemmOut<T> p{(const T*)proj, proj_parts, n_parts, part_stride};
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(conv_delta_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        int rc = crane_launch(conv_delta_prep_kernel<T>, dim3(n_tokens), dim3(256), smem, st, p, cols, tok_entry,
+        int rc = crane_launch(conv_delta_prep_kernel<T>, dim3(n_tokens, by), dim3(256), 0, st, p, cols, tok_entry,
                               cu_q, kv_len, slots, n_slots, (const float*)state, slot_stride, conv_off, conv_w,
                               taps, a_log, dt_bias, aux, aux_cols, H, G, d, dv, key_eps, q_scale, err);
         if (rc != 0 || taps == 1) return rc;
@@ -352,7 +392,9 @@ CRANE_API int crane_decay_gate_prep(int dtype, const void* proj, const float* pr
     if (rank < 0 || rank > 8192) return (int)cudaErrorInvalidValue;
     DISPATCH_T(dtype, {
         GemmOut<T> p{(const T*)proj, proj_parts, n_parts, part_stride};
-        return crane_launch(decay_gate_prep_kernel<T>, dim3(n_tokens), dim3(256), (size_t)(rank > 0 ? rank : 1) * 4,
+        int by = (H * (d > dv ? d : dv) + 255) / 256;            // with few tokens the channels spread over more CTAs
+        while (by > 1 && (long long)n_tokens * by > 4 * 148) by = (by + 1) / 2;
+        return crane_launch(decay_gate_prep_kernel<T>, dim3(n_tokens, by), dim3(256), (size_t)(rank > 0 ? rank : 1) * 4,
                             st, p, cols, tok_entry, a2t, bias, rank, inv_tau, q_scale, aux, aux_cols, H, d, dv);
     });
 }
@@ -377,14 +419,24 @@ CRANE_API int crane_matrix_state_scan(const float* aux, int aux_cols, int q_off,
     if (crane_matrix_state_plan(dk, &rows, &lanes) || dv <= 0 || qk_rep <= 0) return (int)cudaErrorInvalidValue;
     int cpb = 256 / lanes;
     if (cpb > dv) cpb = dv;
+    // few entries and heads: narrower blocks of columns, so that more SMs walk (a column's result does not
+    // depend on the block it is in)
+    while ((long long)n_entries * H * ((dv + cpb - 1) / cpb) < 148 && cpb > 8) cpb /= 2;
     const int blocks = (dv + cpb - 1) / cpb;
     const int threads = ((cpb * lanes + 31) / 32) * 32;
-    const size_t smem = (size_t)SCAN_TOKENS * (3 * dk + cpb + 2) * sizeof(float);
-    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    auto kern = rows == 8 ? matrix_state_scan_kernel<8> : matrix_state_scan_kernel<16>;
+    const size_t per_token = (size_t)((3 * dk + cpb + 2 + 3) & ~3) * sizeof(float);
+    const int vec4 = (dk % 4 == 0 && dv % 4 == 0 && cpb % 4 == 0 && aux_cols % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 &&
+                      v_off % 4 == 0 && (!w_vec || w_off % 4 == 0) && (uintptr_t)aux % 16 == 0) ? 1 : 0;
+    int tile_tokens = (int)((48 * 1024) / (2 * per_token));
+    if (tile_tokens > SCAN_TOKENS) tile_tokens = SCAN_TOKENS;
+    if (tile_tokens < 1) return (int)cudaErrorInvalidValue;
+    const size_t smem = 2 * (size_t)tile_tokens * per_token;
+    const bool full = rows * lanes == dk;
+    auto kern = rows == 8 ? (full ? matrix_state_scan_kernel<8, true> : matrix_state_scan_kernel<8, false>)
+                          : (full ? matrix_state_scan_kernel<16, true> : matrix_state_scan_kernel<16, false>);
     return crane_launch(kern, dim3(n_entries, H, blocks), dim3(threads), smem, st, aux, aux_cols, q_off, k_off, v_off,
                         w_off, beta_off, w_vec, delta, qk_rep, cu_q, kv_len, slots, n_slots, state, slot_stride,
-                        o_raw, H, dk, dv, lanes, cpb, err);
+                        o_raw, H, dk, dv, lanes, cpb, tile_tokens, vec4, err);
 }
 
 CRANE_API int crane_head_norm_gate(int dtype, const float* o_raw, const void* proj, const float* proj_parts,
@@ -404,7 +456,7 @@ CRANE_API int crane_head_talk_mix(int dtype, const float* cross, const float* ta
                                   int n_tokens, int H, int G, int dv, int out_head, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (G <= 0 || H % G || out_head > dv) return (int)cudaErrorInvalidValue;
-    DISPATCH_T(dtype, return crane_launch(head_talk_mix_kernel<T>, dim3(n_tokens), dim3(256), 0, st, cross, talk,
+    DISPATCH_T(dtype, return crane_launch(head_talk_mix_kernel<T>, dim3(n_tokens, H), dim3(out_head > 64 ? 128 : 64), 0, st, cross, talk,
                                           tok_entry, (T*)out, H, G, dv, out_head));
 }
 

@@ -47,7 +47,7 @@ def random_tensors(manifest: Dict[str, TensorSpec], seed: int, dtype: torch.dtyp
         elif spec.init == "offset":
             out[name] = std * t
         elif spec.init == "eye":
-            out[name] = torch.eye(shape[0], shape[1]) + std * t       # a mixing matrix near the identity
+            out[name] = torch.eye(shape[0], shape[1], device=dev) + std * t       # a mixing matrix near the identity
         elif spec.init == "unit":
             out[name] = 0.5 * t
         elif spec.keep == "float32":
