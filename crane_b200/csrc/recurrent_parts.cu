@@ -19,6 +19,8 @@
 // two mixers side by side.
 // The state lives in 32-bit in the request's slot, in the order the scan's threads hold it:
 // [head][row / LANES][column][row % LANES]; a request whose first token is in the step starts from zero.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -178,14 +180,35 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
                  : "memory");
 }
 constexpr int SCAN_TOKENS = 16;
-// FULL: the lanes' rows are exactly the dk rows, and no row is tested.
-template <int ROWS, bool FULL>
-__global__ void __launch_bounds__(256)
+// The sum over the LANES (a power of two, aligned in the warp) that share a column; LANES 0: `lanes` at run
+// time.
+template <int LANES>
+__device__ __forceinline__ float lanes_sum(float x, int lanes) {
+    if (LANES > 0) {
+#pragma unroll
+        for (int o = LANES >> 1; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        return x;
+    }
+    if (lanes > 16) x += __shfl_xor_sync(0xffffffffu, x, 16);
+    if (lanes > 8) x += __shfl_xor_sync(0xffffffffu, x, 8);
+    if (lanes > 4) x += __shfl_xor_sync(0xffffffffu, x, 4);
+    if (lanes > 2) x += __shfl_xor_sync(0xffffffffu, x, 2);
+    if (lanes > 1) x += __shfl_xor_sync(0xffffffffu, x, 1);
+    return x;
+}
+// A lane holds ROWS neighbouring rows of its column.  FULL: the lanes' rows are exactly the dk rows; no row
+// is tested and a lane reads its part of a vector 16 bytes at a time.  WVEC: a decay per row (else one per
+// head).  DELTA: the delta rule's correction.  LANES: the lanes of a column when the kernel is compiled for
+// them (0: any).  The first `walkers` threads walk the tokens; one more warp does nothing but copy the next
+// tile of tokens into shared memory meanwhile, since a walking warp's time is its instructions per token.
+template <int ROWS, bool FULL, bool DELTA, bool WVEC, int LANES>
+__global__ void __launch_bounds__(288)
 matrix_state_scan_kernel(const float* __restrict__ aux, int aux_cols, int q_off, int k_off, int v_off, int w_off,
-                         int beta_off, int w_vec, int delta, int qk_rep, const int* __restrict__ cu_q,
+                         int beta_off, int qk_rep, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_len, const int* __restrict__ slots, int n_slots,
                          float* __restrict__ state, long long slot_stride, float* __restrict__ o_raw,
-                         int H, int dk, int dv, int lanes, int cols_per_block, int tile_tokens, int vec4, int* err) {
+                         int H, int dk, int dv, int lanes_rt, int cols_per_block, int tile_tokens, int vec4,
+                         int walkers, int* err) {
     extern __shared__ __align__(16) float tile[];     // two tiles of [tile_tokens][3 dk + cols + 2, to a multiple of 4]
     pdl_launch_dependents();
     pdl_wait();
@@ -197,87 +220,134 @@ matrix_state_scan_kernel(const float* __restrict__ aux, int aux_cols, int q_off,
         if (threadIdx.x == 0) atomicOr(err, CRANE_ERR_SLOT_RANGE);
         return;
     }
+    const int lanes = LANES > 0 ? LANES : lanes_rt;
     const int start = kv_len[e] - q_len;
-    const int lane = threadIdx.x % lanes, cl = threadIdx.x / lanes;
-    const int col = blockIdx.z * cols_per_block + cl;
-    const bool live = cl < cols_per_block && col < dv;
     const int hq = h / qk_rep;
     const int stride = (3 * dk + cols_per_block + 2 + 3) & ~3;       // rows start on 16 bytes
     const int c0 = blockIdx.z * cols_per_block;
-    const int wib = threadIdx.x >> 5, wl = threadIdx.x & 31, nw = blockDim.x >> 5;
-    // a warp per token; each of a token's vectors is one run of the row, copied 16 bytes a lane (`vec4`: every
-    // run starts on 16 bytes and is a multiple of them) or 4
-    auto run = [&](float* dst, const float* src, int n) {
-        if (vec4) for (int j = wl * 4; j < n; j += 128) cp_async16(dst + j, src + j);
-        else for (int j = wl; j < n; j += 32) cp_async4(dst + j, src + j);
+    const int tile_floats = tile_tokens * stride;
+    const int n_tiles = (q_len + tile_tokens - 1) / tile_tokens;
+    const bool producer = (int)threadIdx.x >= walkers;
+
+    // ---- the copying warp: a token's vectors are runs of its row; units of 16 bytes (`vec4`: every run starts
+    // on 16 bytes and is a multiple of them) or of 4
+    const int wl = threadIdx.x & 31;
+    const int unit = vec4 ? 4 : 1;
+    const int nq = dk / unit, nvu = min(cols_per_block, dv - c0) / unit;
+    const int n_units = (WVEC ? 3 : 2) * nq + nvu;
+    auto place = [&](int x, int& so, int& dofs) {                    // unit x of a token: where from, where to
+        if (x < nq) so = q_off + hq * dk + x * unit, dofs = x * unit;
+        else if (x < 2 * nq) so = k_off + hq * dk + (x - nq) * unit, dofs = dk + (x - nq) * unit;
+        else if (WVEC && x < 3 * nq) so = w_off + hq * dk + (x - 2 * nq) * unit, dofs = 2 * dk + (x - 2 * nq) * unit;
+        else {
+            const int y = x - (WVEC ? 3 : 2) * nq;
+            so = v_off + h * dv + c0 + y * unit, dofs = 3 * dk + y * unit;
+        }
     };
+    auto copy = [&](float* dst, const float* src) {
+        if (vec4) cp_async16(dst, src);
+        else cp_async4(dst, src);
+    };
+    int so0 = -1, do0 = 0, so1 = -1, do1 = 0;                         // the lane's first two units, the same for every token
+    if (producer) {
+        if (wl < n_units) place(wl, so0, do0);
+        if (wl + 32 < n_units) place(wl + 32, so1, do1);
+    }
     auto fetch = [&](int t0, float* buf) {
         const int nt = min(tile_tokens, q_len - t0);
-        for (int tt = wib; tt < nt; tt += nw) {
-            const float* a = aux + (long long)(first + t0 + tt) * aux_cols;
-            float* b = buf + tt * stride;
-            run(b, a + q_off + hq * dk, dk);
-            run(b + dk, a + k_off + hq * dk, dk);
-            if (w_vec) run(b + 2 * dk, a + w_off + hq * dk, dk);
-            const int nv = min(cols_per_block, dv - c0);
-            run(b + 3 * dk, a + v_off + h * dv + c0, nv);
+        const float* a = aux + (long long)(first + t0) * aux_cols;
+        float* b = buf;
+        for (int tt = 0; tt < nt; ++tt, a += aux_cols, b += stride) {
+            if (so0 >= 0) copy(b + do0, a + so0);
+            if (so1 >= 0) copy(b + do1, a + so1);
+            for (int x = wl + 64; x < n_units; x += 32) {
+                int so, dofs;
+                place(x, so, dofs);
+                copy(b + dofs, a + so);
+            }
             if (wl == 0) {
-                if (w_vec) b[3 * dk + cols_per_block] = 1.f;
+                if (WVEC) b[3 * dk + cols_per_block] = 1.f;
                 else cp_async4(b + 3 * dk + cols_per_block, a + w_off + h);
             } else if (wl == 1) {
-                if (delta) cp_async4(b + 3 * dk + cols_per_block + 1, a + beta_off + h);
+                if (DELTA) cp_async4(b + 3 * dk + cols_per_block + 1, a + beta_off + h);
                 else b[3 * dk + cols_per_block + 1] = 1.f;
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     };
-    fetch(0, tile);
+    if (producer) fetch(0, tile);
+
+    // ---- the walkers
+    const int lane = threadIdx.x % lanes, cl = threadIdx.x / lanes;
+    const int r0 = lane * ROWS;                       // the lane's rows: r0 .. r0 + ROWS - 1
+    const int col = c0 + cl;
+    const bool live = !producer && cl < cols_per_block && col < dv;
+    const int vcol = live ? cl : 0;
     // state [H][ROWS][dv][lanes]
     float* sp = state + (long long)slot * slot_stride + (long long)h * ROWS * dv * lanes;
     float s[ROWS];
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
-        s[i] = (live && start > 0) ? sp[((long long)i * dv + col) * lanes + lane] : 0.f;
-    const int tile_floats = tile_tokens * stride;
-    for (int t0 = 0, it = 0; t0 < q_len; t0 += tile_tokens, ++it) {
+        s[i] = (live && start > 0 && (FULL || r0 + i < dk)) ? sp[((long long)i * dv + col) * lanes + lane] : 0.f;
+    __syncthreads();                                  // the first tile is there
+    const long long o_step = (long long)H * dv;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int t0 = it * tile_tokens;
         const int nt = min(tile_tokens, q_len - t0);
-        const float* cur = tile + (it & 1) * tile_floats;
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();              // the tile is there for all; all have left the other one
-        if (t0 + tile_tokens < q_len) fetch(t0 + tile_tokens, tile + ((it + 1) & 1) * tile_floats);
+        if (producer) {
+            if (it + 1 < n_tiles) fetch(t0 + tile_tokens, tile + ((it + 1) & 1) * tile_floats);
+        } else {
+            const float* tp = tile + (it & 1) * tile_floats;
+            float* op = o_raw + (long long)(first + t0) * o_step + h * dv + (live ? col : 0);
 #pragma unroll(ROWS == 8 ? 2 : 1)
-        for (int tt = 0; tt < nt; ++tt) {
-            const float* q = cur + tt * stride;
-            const float* k = q + dk;
-            const float* w = k + dk;
-            const float vv = live ? q[3 * dk + cl] : 0.f;
-            const float ws = q[3 * dk + cols_per_block], beta = q[3 * dk + cols_per_block + 1];
-            float dot = 0.f;
+            for (int tt = 0; tt < nt; ++tt, tp += stride, op += o_step) {
+                float qv[ROWS], kv[ROWS], wv[ROWS];
+                if (FULL) {                            // lane's rows are one aligned run of each vector
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int r = lane + i * lanes;
-                if (FULL || r < dk) {
-                    s[i] *= w_vec ? w[r] : ws;
-                    dot = fmaf(s[i], k[r], dot);
-                }
-            }
-            float u = vv;
-            if (delta) {
-                for (int o = lanes >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                u = beta * (vv - dot);
-            }
-            float rd = 0.f;
+                    for (int i = 0; i < ROWS; i += 4) {
+                        const float4 a4 = *reinterpret_cast<const float4*>(tp + r0 + i);
+                        const float4 b4 = *reinterpret_cast<const float4*>(tp + dk + r0 + i);
+                        qv[i] = a4.x, qv[i + 1] = a4.y, qv[i + 2] = a4.z, qv[i + 3] = a4.w;
+                        kv[i] = b4.x, kv[i + 1] = b4.y, kv[i + 2] = b4.z, kv[i + 3] = b4.w;
+                        if (WVEC) {
+                            const float4 c4 = *reinterpret_cast<const float4*>(tp + 2 * dk + r0 + i);
+                            wv[i] = c4.x, wv[i + 1] = c4.y, wv[i + 2] = c4.z, wv[i + 3] = c4.w;
+                        }
+                    }
+                } else {                               // rows past dk: zeros, and their state stays zero
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int r = lane + i * lanes;
-                if (FULL || r < dk) {
-                    s[i] = fmaf(k[r], u, s[i]);
-                    rd = fmaf(s[i], q[r], rd);
+                    for (int i = 0; i < ROWS; ++i) {
+                        const bool in = r0 + i < dk;
+                        qv[i] = in ? tp[r0 + i] : 0.f;
+                        kv[i] = in ? tp[dk + r0 + i] : 0.f;
+                        if (WVEC) wv[i] = in ? tp[2 * dk + r0 + i] : 0.f;
+                    }
                 }
+                const float vv = tp[3 * dk + vcol];    // a column that is not live reads a neighbour's and writes nothing
+                const float ws = WVEC ? 1.f : tp[3 * dk + cols_per_block];
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < ROWS; ++i) {
+                    s[i] *= WVEC ? wv[i] : ws;
+                    if (DELTA) dot = fmaf(s[i], kv[i], dot);
+                }
+                float u = vv;
+                if (DELTA) {
+                    dot = lanes_sum<LANES>(dot, lanes);
+                    u = tp[3 * dk + cols_per_block + 1] * (vv - dot);
+                }
+                float rd = 0.f;
+#pragma unroll
+                for (int i = 0; i < ROWS; ++i) {
+                    s[i] = fmaf(kv[i], u, s[i]);
+                    rd = fmaf(s[i], qv[i], rd);
+                }
+                rd = lanes_sum<LANES>(rd, lanes);
+                if (live && lane == 0) *op = rd;
             }
-            for (int o = lanes >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
-            if (live && lane == 0) o_raw[(long long)(first + t0 + tt) * H * dv + h * dv + col] = rd;
         }
+        __syncthreads();              // the next tile is there for all; all have left this one
     }
     if (live) {
 #pragma unroll
@@ -423,7 +493,7 @@ CRANE_API int crane_matrix_state_scan(const float* aux, int aux_cols, int q_off,
     // depend on the block it is in)
     while ((long long)n_entries * H * ((dv + cpb - 1) / cpb) < 148 && cpb > 8) cpb /= 2;
     const int blocks = (dv + cpb - 1) / cpb;
-    const int threads = ((cpb * lanes + 31) / 32) * 32;
+    const int walkers = ((cpb * lanes + 31) / 32) * 32;        // and a warp that copies
     const size_t per_token = (size_t)((3 * dk + cpb + 2 + 3) & ~3) * sizeof(float);
     const int vec4 = (dk % 4 == 0 && dv % 4 == 0 && cpb % 4 == 0 && aux_cols % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 &&
                       v_off % 4 == 0 && (!w_vec || w_off % 4 == 0) && (uintptr_t)aux % 16 == 0) ? 1 : 0;
@@ -432,11 +502,24 @@ CRANE_API int crane_matrix_state_scan(const float* aux, int aux_cols, int q_off,
     if (tile_tokens < 1) return (int)cudaErrorInvalidValue;
     const size_t smem = 2 * (size_t)tile_tokens * per_token;
     const bool full = rows * lanes == dk;
-    auto kern = rows == 8 ? (full ? matrix_state_scan_kernel<8, true> : matrix_state_scan_kernel<8, false>)
-                          : (full ? matrix_state_scan_kernel<16, true> : matrix_state_scan_kernel<16, false>);
-    return crane_launch(kern, dim3(n_entries, H, blocks), dim3(threads), smem, st, aux, aux_cols, q_off, k_off, v_off,
-                        w_off, beta_off, w_vec, delta, qk_rep, cu_q, kv_len, slots, n_slots, state, slot_stride,
-                        o_raw, H, dk, dv, lanes, cpb, tile_tokens, vec4, err);
+    using Kern = decltype(&matrix_state_scan_kernel<8, true, true, true, 0>);
+    auto pick = [&](auto rows_c, auto lanes_c) -> Kern {
+        constexpr int R = decltype(rows_c)::value, L = decltype(lanes_c)::value;
+        if (full) return delta ? (w_vec ? matrix_state_scan_kernel<R, true, true, true, L> : matrix_state_scan_kernel<R, true, true, false, L>)
+                               : (w_vec ? matrix_state_scan_kernel<R, true, false, true, L> : matrix_state_scan_kernel<R, true, false, false, L>);
+        return delta ? (w_vec ? matrix_state_scan_kernel<R, false, true, true, 0> : matrix_state_scan_kernel<R, false, true, false, 0>)
+                     : (w_vec ? matrix_state_scan_kernel<R, false, false, true, 0> : matrix_state_scan_kernel<R, false, false, false, 0>);
+    };
+    using std::integral_constant;
+    Kern kern;
+    if (rows != 8) kern = pick(integral_constant<int, 16>{}, integral_constant<int, 0>{});
+    else if (full && lanes == 4) kern = pick(integral_constant<int, 8>{}, integral_constant<int, 4>{});      // heads of 32,
+    else if (full && lanes == 8) kern = pick(integral_constant<int, 8>{}, integral_constant<int, 8>{});      // 64
+    else if (full && lanes == 16) kern = pick(integral_constant<int, 8>{}, integral_constant<int, 16>{});    // and 128
+    else kern = pick(integral_constant<int, 8>{}, integral_constant<int, 0>{});
+    return crane_launch(kern, dim3(n_entries, H, blocks), dim3(walkers + 32), smem, st, aux, aux_cols, q_off, k_off,
+                        v_off, w_off, beta_off, qk_rep, cu_q, kv_len, slots, n_slots, state, slot_stride,
+                        o_raw, H, dk, dv, lanes, cpb, tile_tokens, vec4, walkers, err);
 }
 
 CRANE_API int crane_head_norm_gate(int dtype, const float* o_raw, const void* proj, const float* proj_parts,
