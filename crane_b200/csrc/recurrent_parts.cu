@@ -413,18 +413,35 @@ pair_norm_mean_kernel(GemmOut<T> a, GemmOut<T> b, const float* __restrict__ wa, 
     pdl_wait();
     const long long base = (long long)blockIdx.x * hidden;
     float sa = 0.f, sb = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float x = a.load(base + c), y = b.load(base + c);
-        row2[c] = x;
-        row2[hidden + c] = y;
-        sa = fmaf(x, x, sa);
-        sb = fmaf(y, y, sb);
+    const bool pairs = (hidden & 1) == 0;             // rows of even length: two neighbours a load and a store
+    if (pairs) {
+        for (int c = 2 * threadIdx.x; c < hidden; c += 2 * blockDim.x) {
+            const float2 x = a.load2(base + c), y = b.load2(base + c);
+            row2[c] = x.x, row2[c + 1] = x.y;
+            row2[hidden + c] = y.x, row2[hidden + c + 1] = y.y;
+            sa = fmaf(x.x, x.x, fmaf(x.y, x.y, sa));
+            sb = fmaf(y.x, y.x, fmaf(y.y, y.y, sb));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float x = a.load(base + c), y = b.load(base + c);
+            row2[c] = x;
+            row2[hidden + c] = y;
+            sa = fmaf(x, x, sa);
+            sb = fmaf(y, y, sb);
+        }
     }
     sa = block_sum(sa, scratch);
     sb = block_sum(sb, scratch);
     const float ra = rsqrtf(sa / (float)hidden + eps), rb = rsqrtf(sb / (float)hidden + eps);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
-        out[base + c] = from_f32<T>(0.5f * (row2[c] * ra * wa[c] + row2[hidden + c] * rb * wb[c]));
+    if (pairs) {
+        for (int c = 2 * threadIdx.x; c < hidden; c += 2 * blockDim.x)
+            st2(out + base + c, 0.5f * (row2[c] * ra * wa[c] + row2[hidden + c] * rb * wb[c]),
+                0.5f * (row2[c + 1] * ra * wa[c + 1] + row2[hidden + c + 1] * rb * wb[c + 1]));
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+            out[base + c] = from_f32<T>(0.5f * (row2[c] * ra * wa[c] + row2[hidden + c] * rb * wb[c]));
+    }
 }
 
 }  // namespace
