@@ -401,7 +401,7 @@ PLAN_LENS = [37, 1, 9, 11]
 
 @pytest.mark.parametrize("delta", [False, True])
 @pytest.mark.parametrize("H, G, dk, dv", [(2, 2, 16, 8), (4, 2, 24, 40), (1, 1, 64, 32), (6, 3, 48, 16), (2, 1, 128, 128),
-                                          (1, 1, 300, 20)])
+                                          (1, 1, 300, 20), (2, 2, 32, 8), (3, 1, 32, 12), (2, 2, 256, 4)])
 def test_matrix_state_scan(K, delta, H, G, dk, dv):
     """Both recurrences over portions, single tokens and a slot that is used again, from a state pool
     full of another request's numbers.  The decays stay near 1 and the first token's key and value
