@@ -65,8 +65,11 @@ class CachePools:
         if len(pages_per_group) != len(keys):
             raise ValueError("one page count per layer group is needed")
         self.groups = [GroupSpec(pages_per_group[g], page_size, keys[g][2]) for g in range(len(keys))]
+        # A model none of whose layers holds pages (recurrent layers only) still has the table count its
+        # requests' tokens and hand out state slots: one group of page numbers that stand for no storage
+        # and do not run out.
         self.table = PageTable(self.groups, max_requests) if keys else PageTable(
-            [GroupSpec(0, page_size, 0)], max_requests)
+            [GroupSpec(1 << 20, page_size, 0)], max_requests)
         self.page_size = page_size
         def storage(need: CacheNeed) -> LayerCache:
             if need.kind == "multi":

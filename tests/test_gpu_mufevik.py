@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 LENGTHS = {"MA": [1, 2, 19, 100, 65, 48, 33], "MB": [5, 41, 97, 230, 129, 64], "MC": [3, 70, 130, 17],
-           "MD": [2, 150, 31, 16, 77], "ML": [7, 150, 300, 64]}
+           "MD": [2, 150, 31, 16, 77], "ME": [1, 90, 33, 2, 64], "MF": [4, 120, 8, 57], "ML": [7, 150, 300, 64]}
 
 
 @pytest.fixture(scope="module")
@@ -60,7 +60,7 @@ def _compare(got, tb, plain, dtype, label, tol_rms=3e-5):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD"])
+@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD", "ME", "MF"])
 def test_alone_whole_tail_portions(name, dtype, cases, tmp_path):
     folder, reqs, plain = cases(name, dtype)
     ps = tm.TINY[name]["page_size"]
@@ -75,7 +75,7 @@ def test_alone_whole_tail_portions(name, dtype, cases, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD"])
+@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD", "ME", "MF"])
 def test_mixed_with_page_and_slot_reuse(name, dtype, cases, tmp_path):
     folder, reqs, plain = cases(name, dtype)
     ps = tm.TINY[name]["page_size"]
@@ -533,7 +533,7 @@ def _greedy(n):
     return GenerationConfig(max_new_tokens=n, temperature=None, eos_token_id=-1)
 
 
-@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD"])
+@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD", "ME", "MF"])
 def test_greedy_generation_float32_equals_plain(name, model_folders):
     folder = model_folders(name, "float32")
     cfg, w = pm.load_folder(folder)

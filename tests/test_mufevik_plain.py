@@ -208,7 +208,7 @@ def folders(tmp_path_factory):
     return get
 
 
-@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD"])
+@pytest.mark.parametrize("name", ["MA", "MB", "MC", "MD", "ME", "MF"])
 def test_cut_anywhere_the_logits_stay(name, folders):
     cfg, w = folders(name)
     rng = np.random.default_rng(1)

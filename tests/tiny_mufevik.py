@@ -77,6 +77,27 @@ MD = {
     ],
 }
 
+# layers of the delta rule only (no layer asks for pages); one query/key head per head and one for all
+ME = {
+    "architecture": "Mufevik", "vocab": 83, "width": 56, "norm": {"eps": 1e-5}, "streams": 2, "logit_scale": 3.0,
+    "layers": [
+        {"type": "delta", "mixer": _delta(2, 2, 32, 12, 2), "mlp": _moe(5, 2, 0, 0, 12, 8)},
+        {"type": "delta", "mixer": _delta(3, 1, 24, 16, 3), "mlp": None},
+    ],
+}
+
+# pairs only; as many key/value heads as query heads, the whole head rotated, keys as wide as values;
+# a single attention head in the second layer
+MF = {
+    "architecture": "Mufevik", "vocab": 150, "width": 72, "norm": {"eps": 1e-6}, "streams": 3,
+    "layers": [
+        {"type": "parallel", "mixer": {"left": _left(3, 3, 16, 16, 0.25, 16, 3000.0), "right": _right(1, 16, 16, 5.0, 4)},
+         "mlp": _moe(6, 3, 2, 2, 16, 24)},
+        {"type": "parallel", "mixer": {"left": _left(1, 1, 48, 48, 0.15, 48, 3000.0), "right": _right(3, 8, 24, 1.5, 3)},
+         "mlp": None},
+    ],
+}
+
 # layer sizes at which the tensor-core kernels are taken
 ML = {
     "architecture": "Mufevik", "vocab": 512, "width": 512, "norm": {"eps": 1e-5}, "streams": 3, "logit_scale": 0.75,
@@ -93,5 +114,7 @@ TINY = {
     "MB": {"config": MB, "seed": 32, "std": 0.1, "norm_std": 0.05, "page_size": 8},
     "MC": {"config": MC, "seed": 33, "std": 0.1, "norm_std": 0.05, "page_size": 32},
     "MD": {"config": MD, "seed": 34, "std": 0.12, "norm_std": 0.05, "page_size": 16},
+    "ME": {"config": ME, "seed": 36, "std": 0.12, "norm_std": 0.05, "page_size": 16},
+    "MF": {"config": MF, "seed": 37, "std": 0.1, "norm_std": 0.05, "page_size": 8},
     "ML": {"config": ML, "seed": 35, "std": 0.03, "norm_std": 0.05, "page_size": 64},
 }
