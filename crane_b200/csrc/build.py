@@ -33,7 +33,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # "file@NAME=VALUE": the file compiled once more with -DNAME=VALUE into an object of its own.  The
 # warp-level attention kernels are compiled per head size this way, side by side.
 ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
-BASE_SOURCES = ["elementwise.cu", "layer_parts.cu", "stream_parts.cu", "mixer_parts.cu", "hyper_parts.cu", "recurrent_parts.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
+BASE_SOURCES = ["elementwise.cu", "layer_parts.cu", "stream_parts.cu", "mixer_parts.cu", "hyper_parts.cu", "recurrent_parts.cu", "scored_parts.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
                 "latent_attention.cu", "latent_attention_mma.cu", "attention_decode.cu", "attention_prefill.cu",
                 "attention_prefill_tc.cu", "sampling.cu"]
 # the two files whose entry points pick a head size's launcher: compiled for the library's set of sizes

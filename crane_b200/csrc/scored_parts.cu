@@ -1,0 +1,395 @@
+// Kernels around attention whose scores are worked on before they become weights, and of the block
+// that holds it.
+//
+// 1. `add_group_rmsnorm`: x += (a + f), the two results of a block whose sublayers read the same norm,
+//    then RMS norm in groups: the row in `groups` equal consecutive parts, each over the root of its own
+//    mean square (+ eps), the whole times w.
+// 2. `poly_norm`: act(z) = a N(z) + b N(z^2) + c N(z^3) + e over a token's row of a feed-forward, N dividing
+//    by the root of the mean square of what it is given.
+// 3. `scored_prep`: a token's row [q | k | v | gate] of the merged projection -> the query rows for the
+//    attention kernel, the token's key and value rows in the pages, sigmoid(gate) per head.  On the way:
+//    a causal convolution of a few taps over time on every channel (the inputs of the taps - 1 positions
+//    before the step come from the request's state slot), RMS norm of q and of k over their whole rows,
+//    rotation of the leading `rot_dims` elements of every head (element i with i + rot_dims / 2).  A head
+//    may hold several maps of `dim` elements (differential attention: two); each map turns like a head of
+//    its own.  Stored heads may be wider than they are (zero-filled), so that kernels compiled for one
+//    head size serve.  `conv_tail_update` then replaces the slot's last taps - 1 inputs.
+// 4. `head_finish`: what follows the weighted sums of a head: o = a1 - lambda a2 for two maps, o over the
+//    root of its mean square times a constant, times the head's gate.
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------ residual + norm in groups
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_group_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> a, int has_a, GemmOut<T> f, int has_f,
+                         const float* __restrict__ w, const int* __restrict__ rows, T* __restrict__ out,
+                         int width, int groups, float eps) {
+    extern __shared__ float row[];                    // [width]
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const long long base = (long long)(rows != nullptr ? rows[r] : r) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = x[base + c];
+        if (has_a || has_f) {
+            // the two results are added to one another first, then to the stream
+            const float d = (has_a ? a.load(base + c) : 0.f) + (has_f ? f.load(base + c) : 0.f);
+            v += d;
+            if (rows == nullptr) x[base + c] = v;
+        }
+        row[c] = v;
+    }
+    __syncthreads();
+    const int gsize = width / groups;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    T* o = out + (long long)r * width;
+    if (groups >= nwarps) {
+        for (int g = warp; g < groups; g += nwarps) {
+            const float* p = row + g * gsize;
+            float ss = 0.f;
+            for (int c = lane; c < gsize; c += 32) ss = fmaf(p[c], p[c], ss);
+            const float rstd = rsqrtf(warp_sum(ss) / (float)gsize + eps);
+            for (int c = lane; c < gsize; c += 32) o[g * gsize + c] = from_f32<T>(p[c] * rstd * w[g * gsize + c]);
+        }
+        return;
+    }
+    for (int g = 0; g < groups; ++g) {
+        const float* p = row + g * gsize;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < gsize; c += blockDim.x) ss = fmaf(p[c], p[c], ss);
+        const float rstd = rsqrtf(block_sum(ss, scratch) / (float)gsize + eps);
+        for (int c = threadIdx.x; c < gsize; c += blockDim.x)
+            o[g * gsize + c] = from_f32<T>(p[c] * rstd * w[g * gsize + c]);
+    }
+}
+
+// ------------------------------------------------------ PolyNorm
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_kernel(GemmOut<T> up, const float* __restrict__ coef, T* __restrict__ out, int F, float eps) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long base = (long long)blockIdx.x * F;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    if ((F & 1) == 0) {
+        for (int c = 2 * threadIdx.x; c < F; c += 2 * blockDim.x) {
+            const float2 z = up.load2(base + c);
+            const float a = z.x * z.x, b = z.y * z.y;
+            s2 += a + b;
+            s4 += a * a + b * b;
+            s6 += a * a * a + b * b * b;
+        }
+    } else {
+        for (int c = threadIdx.x; c < F; c += blockDim.x) {
+            const float z = up.load(base + c), a = z * z;
+            s2 += a;
+            s4 += a * a;
+            s6 += a * a * a;
+        }
+    }
+    s2 = block_sum(s2, scratch);
+    s4 = block_sum(s4, scratch);
+    s6 = block_sum(s6, scratch);
+    const float inv = 1.f / (float)F;
+    const float r1 = coef[0] * rsqrtf(s2 * inv + eps), r2 = coef[1] * rsqrtf(s4 * inv + eps),
+                r3 = coef[2] * rsqrtf(s6 * inv + eps), e = coef[3];
+    if ((F & 1) == 0) {
+        for (int c = 2 * threadIdx.x; c < F; c += 2 * blockDim.x) {
+            const float2 z = up.load2(base + c);
+            st2(out + base + c, fmaf(z.x, fmaf(z.x, fmaf(z.x, r3, r2), r1), e),
+                fmaf(z.y, fmaf(z.y, fmaf(z.y, r3, r2), r1), e));
+        }
+    } else {
+        for (int c = threadIdx.x; c < F; c += blockDim.x) {
+            const float z = up.load(base + c);
+            out[base + c] = from_f32<T>(fmaf(z, fmaf(z, fmaf(z, r3, r2), r1), e));
+        }
+    }
+}
+
+// ------------------------------------------------------ projection -> queries, pages
+struct PrepArgs {
+    int cols;                       // columns of a row of the merged projection
+    const int* positions;
+    const int* tok_entry;
+    const int* cu_q;
+    const int* kv_len;
+    const int* slots;
+    int n_slots;
+    const float* tails;             // [slots][taps - 1][C]: the convolutions' last inputs (null: no convolution)
+    long long slot_stride;
+    const float* conv_w;            // [C][taps]
+    int taps;
+    const int* block_table;
+    int max_blocks, num_pages, page_size;
+    const float* qw;                // norm weights over the whole q / k rows, or null
+    const float* kw;
+    float eps;
+    void* q_out;                    // [n][H][dk_store]
+    void* k_pool;                   // [pages][G][page_size][dk_store]
+    void* v_pool;                   // [pages][G][page_size][dv_store]
+    int H, G, maps, dim, dv;        // a query / key head holds `maps` maps of `dim` elements, a value head dv
+    int dk_store, dpad, dv_store;   // stored widths; map i of a head starts at i * dpad
+    const float* cos_tab;
+    const float* sin_tab;
+    int n_positions, rot_dims;
+    float* gate_out;                // [n][H] sigmoid of the gate columns, or null
+    int gate_col;                   // where they start in the row
+    int* err;
+};
+
+// One stored head row of queries or keys: norm factor and weight, rotation.  sm: the token's channels
+// after the convolution; ch0: the first channel of the head's map; i: element within the map.
+__device__ __forceinline__ float prep_element(const float* sm, const float* nw, float rn, int ch0, int i, int half,
+                                              const float* ct, const float* sn) {
+    float v = sm[ch0 + i] * rn * (nw != nullptr ? nw[ch0 + i] : 1.f);
+    if (i < 2 * half) {
+        const int j = i < half ? i + half : i - half, a = i < half ? i : i - half;
+        const float o = sm[ch0 + j] * rn * (nw != nullptr ? nw[ch0 + j] : 1.f);
+        v = i < half ? v * ct[a] - o * sn[a] : v * ct[a] + o * sn[a];
+    }
+    return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
+    extern __shared__ float sm[];                     // [C] the token's q, k, v after the convolution
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int e = a.tok_entry[t];
+    if (e < 0) return;
+    const int Cq = a.H * a.maps * a.dim, Ck = a.G * a.maps * a.dim, Cv = a.G * a.dv, C = Cq + Ck + Cv;
+    const int pos = a.positions[t];
+    const int half = a.cos_tab != nullptr ? a.rot_dims >> 1 : 0;
+    if (half > 0 && (pos < 0 || pos >= a.n_positions)) {
+        if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_POSITION_RANGE);
+        return;
+    }
+    const long long base = (long long)t * a.cols;
+    float sq = 0.f, sk = 0.f;
+    if (a.tails != nullptr && a.taps > 1) {
+        const int first = a.cu_q[e];
+        const int i = t - first;                                      // the token's place in its portion
+        const int start = a.kv_len[e] - (a.cu_q[e + 1] - first);      // tokens of the request before the step
+        const int slot = a.slots[e];
+        if (slot < 0 || slot >= a.n_slots) {
+            if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_SLOT_RANGE);
+            return;
+        }
+        const float* tail = a.tails + (long long)slot * a.slot_stride;
+        const int taps = a.taps;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float acc = 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j;
+                float u = 0.f;
+                if (i - back >= 0) u = proj.load(base - (long long)back * a.cols + c);
+                else if (start + i - back >= 0) u = tail[(long long)(taps - 1 + i - back) * C + c];
+                acc = fmaf(a.conv_w[(long long)c * taps + j], u, acc);
+            }
+            sm[c] = acc;
+            if (c < Cq) sq = fmaf(acc, acc, sq);
+            else if (c < Cq + Ck) sk = fmaf(acc, acc, sk);
+        }
+    } else {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            const float v = proj.load(base + c);
+            sm[c] = v;
+            if (c < Cq) sq = fmaf(v, v, sq);
+            else if (c < Cq + Ck) sk = fmaf(v, v, sk);
+        }
+    }
+    float rq = 1.f, rk = 1.f;
+    if (a.qw != nullptr) rq = rsqrtf(block_sum(sq, scratch) / (float)Cq + a.eps);
+    if (a.kw != nullptr) rk = rsqrtf(block_sum(sk, scratch) / (float)Ck + a.eps);
+    __syncthreads();
+    const float* ct = a.cos_tab + (long long)pos * half;
+    const float* sn = a.sin_tab + (long long)pos * half;
+    T* q_out = (T*)a.q_out + (long long)t * a.H * a.dk_store;
+    for (int c = threadIdx.x; c < a.H * a.dk_store; c += blockDim.x) {
+        const int h = c / a.dk_store, r = c % a.dk_store, mp = r / a.dpad, i = r % a.dpad;
+        float v = 0.f;
+        if (mp < a.maps && i < a.dim) v = prep_element(sm, a.qw, rq, (h * a.maps + mp) * a.dim, i, half, ct, sn);
+        q_out[c] = from_f32<T>(v);
+    }
+    if (a.gate_out != nullptr)
+        for (int h = threadIdx.x; h < a.H; h += blockDim.x)
+            a.gate_out[(long long)t * a.H + h] = 1.f / (1.f + expf(-proj.load(base + a.gate_col + h)));
+    const int blk = pos / a.page_size;
+    const int page = (pos >= 0 && blk < a.max_blocks) ? a.block_table[(long long)e * a.max_blocks + blk] : -1;
+    if (page < 0 || page >= a.num_pages) {
+        if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_PAGE_RANGE);
+        return;
+    }
+    const int place = pos % a.page_size;
+    T* k_pool = (T*)a.k_pool;
+    T* v_pool = (T*)a.v_pool;
+    for (int c = threadIdx.x; c < a.G * a.dk_store; c += blockDim.x) {
+        const int g = c / a.dk_store, r = c % a.dk_store, mp = r / a.dpad, i = r % a.dpad;
+        float v = 0.f;
+        if (mp < a.maps && i < a.dim)
+            v = prep_element(sm + Cq, a.kw, rk, (g * a.maps + mp) * a.dim, i, half, ct, sn);
+        k_pool[(((long long)page * a.G + g) * a.page_size + place) * a.dk_store + r] = from_f32<T>(v);
+    }
+    for (int c = threadIdx.x; c < a.G * a.dv_store; c += blockDim.x) {
+        const int g = c / a.dv_store, i = c % a.dv_store;
+        const float v = i < a.dv ? sm[Cq + Ck + g * a.dv + i] : 0.f;
+        v_pool[(((long long)page * a.G + g) * a.page_size + place) * a.dv_store + i] = from_f32<T>(v);
+    }
+}
+
+// The slot's last taps - 1 inputs after the step.  One thread per (entry, channel) walks the places in
+// order: place j takes what lay q_len places further on (or a row of this step), which no earlier
+// write of the walk has touched.
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_tail_update_kernel(GemmOut<T> proj, int cols, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                        const int* __restrict__ slots, int n_slots, float* __restrict__ tails, long long slot_stride,
+                        int taps, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int first = cu_q[e], q_len = cu_q[e + 1] - first;
+    if (q_len <= 0 || c >= C) return;
+    const int slot = slots[e];
+    if (slot < 0 || slot >= n_slots) return;
+    const int end = kv_len[e], start = end - q_len;
+    float* tail = tails + (long long)slot * slot_stride;
+    for (int j = 0; j < taps - 1; ++j) {
+        const int p = end - (taps - 1) + j;            // the position whose input place j holds afterwards
+        float v = 0.f;
+        if (p >= start) v = proj.load((long long)(first + p - start) * cols + c);
+        else if (p >= 0) v = tail[(long long)(j + q_len) * C + c];
+        tail[(long long)j * C + c] = v;
+    }
+}
+
+// ------------------------------------------------------ after the weighted sums
+// a: float [n][H][maps][dv_in] (the maps' normalised results).  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_finish_kernel(const float* __restrict__ a, const int* __restrict__ tok_entry, const float* __restrict__ gate,
+                   T* __restrict__ out, int n, int H, int maps, int dv, int dv_in, int dv_out, float lambda,
+                   int norm, float norm_scale, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (long long)n * H) return;
+    const int t = (int)(unit / H);
+    if (tok_entry[t] < 0) return;
+    const float* p = a + unit * maps * dv_in;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) {
+        const float o = maps == 2 ? p[c] - lambda * p[dv_in + c] : p[c];
+        ss = fmaf(o, o, ss);
+    }
+    float f = 1.f;
+    if (norm) f = rsqrtf(warp_sum(ss) / (float)dv + eps) * norm_scale;
+    if (gate != nullptr) f *= gate[unit];
+    T* op = out + unit * dv_out;
+    for (int c = lane; c < dv_out; c += 32) {
+        float o = 0.f;
+        if (c < dv) o = (maps == 2 ? p[c] - lambda * p[dv_in + c] : p[c]) * f;
+        op[c] = from_f32<T>(o);
+    }
+}
+
+}  // namespace
+
+CRANE_API int crane_add_group_rmsnorm(int dtype, float* x, const void* a, const float* a_parts, int a_n,
+                                      long long a_stride, const void* f, const float* f_parts, int f_n,
+                                      long long f_stride, const float* w, const int* rows, void* out, int n_rows,
+                                      int width, int groups, float eps, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    if (groups <= 0 || width % groups != 0 || (size_t)width * sizeof(float) > 200 * 1024) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)width * sizeof(float);
+    DISPATCH_T(dtype, {
+        GemmOut<T> ga{(const T*)a, a_parts, a_n, a_stride}, gf{(const T*)f, f_parts, f_n, f_stride};
+        auto kern = add_group_rmsnorm_kernel<T>;
+        if (smem > 48 * 1024) {
+            static size_t configured = 0;
+            if (configured < smem) {
+                if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                    return (int)cudaGetLastError();
+                configured = smem;
+            }
+        }
+        return crane_launch(kern, dim3(n_rows), dim3(256), smem, st, x, ga,
+                            (a != nullptr || a_parts != nullptr) ? 1 : 0, gf,
+                            (f != nullptr || f_parts != nullptr) ? 1 : 0, w, rows, (T*)out, width, groups, eps);
+    });
+}
+
+CRANE_API int crane_poly_norm(int dtype, const void* up, const float* up_parts, int n_parts, long long part_stride,
+                              const float* coef, void* out, int n_rows, int F, float eps, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    DISPATCH_T(dtype, {
+        GemmOut<T> g{(const T*)up, up_parts, n_parts, part_stride};
+        return crane_launch(poly_norm_kernel<T>, dim3(n_rows), dim3(256), 0, st, g, coef, (T*)out, F, eps);
+    });
+}
+
+// Every pointer and size of the preparation in one block of arguments (see PrepArgs); then, with a
+// convolution, the slot's last inputs are replaced by a second kernel.
+CRANE_API int crane_scored_prep(int dtype, const void* proj, const float* proj_parts, int n_parts, long long part_stride,
+                                int cols, const int* positions, const int* tok_entry, const int* cu_q,
+                                const int* kv_len, const int* slots, int n_slots, float* tails, long long slot_stride,
+                                const float* conv_w, int taps, const int* block_table, int max_blocks, int num_pages,
+                                int page_size, const float* qw, const float* kw, float eps, void* q_out, void* k_pool,
+                                void* v_pool, int n_tokens, int n_entries, int H, int G, int maps, int dim, int dv,
+                                int dk_store, int dpad, int dv_store, const float* cos_tab, const float* sin_tab,
+                                int n_positions, int rot_dims, float* gate_out, int gate_col, int* err,
+                                cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const int C = (H + G) * maps * dim + G * dv;
+    if (maps < 1 || dpad < dim || dk_store < maps * dpad || dv_store < dv || taps < 1 || rot_dims > dim ||
+        (size_t)C * sizeof(float) > 200 * 1024)
+        return (int)cudaErrorInvalidValue;
+    PrepArgs a;
+    a.cols = cols; a.positions = positions; a.tok_entry = tok_entry; a.cu_q = cu_q; a.kv_len = kv_len;
+    a.slots = slots; a.n_slots = n_slots; a.tails = taps > 1 ? tails : nullptr; a.slot_stride = slot_stride;
+    a.conv_w = conv_w; a.taps = taps; a.block_table = block_table; a.max_blocks = max_blocks;
+    a.num_pages = num_pages; a.page_size = page_size; a.qw = qw; a.kw = kw; a.eps = eps; a.q_out = q_out;
+    a.k_pool = k_pool; a.v_pool = v_pool; a.H = H; a.G = G; a.maps = maps; a.dim = dim; a.dv = dv;
+    a.dk_store = dk_store; a.dpad = dpad; a.dv_store = dv_store; a.cos_tab = cos_tab; a.sin_tab = sin_tab;
+    a.n_positions = n_positions; a.rot_dims = cos_tab != nullptr ? rot_dims : 0; a.gate_out = gate_out;
+    a.gate_col = gate_col; a.err = err;
+    const size_t smem = (size_t)C * sizeof(float);
+    DISPATCH_T(dtype, {
+        GemmOut<T> g{(const T*)proj, proj_parts, n_parts, part_stride};
+        auto kern = scored_prep_kernel<T>;
+        if (smem > 48 * 1024) {
+            static size_t configured = 0;
+            if (configured < smem) {
+                if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                    return (int)cudaGetLastError();
+                configured = smem;
+            }
+        }
+        int rc = crane_launch(kern, dim3(n_tokens), dim3(256), smem, st, g, a);
+        if (rc != 0 || taps <= 1 || tails == nullptr) return rc;
+        return crane_launch(conv_tail_update_kernel<T>, dim3((C + 127) / 128, n_entries), dim3(128), 0, st, g, cols,
+                            cu_q, kv_len, slots, n_slots, tails, slot_stride, taps, C);
+    });
+}
+
+CRANE_API int crane_head_finish(int dtype, const float* a, const int* tok_entry, const float* gate, void* out, int n,
+                                int H, int maps, int dv, int dv_in, int dv_out, float lambda, int norm,
+                                float norm_scale, float eps, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (maps < 1 || maps > 2 || dv_in < dv || dv_out < dv) return (int)cudaErrorInvalidValue;
+    const long long units = (long long)n * H;
+    DISPATCH_T(dtype, {
+        return crane_launch(head_finish_kernel<T>, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, a, tok_entry,
+                            gate, (T*)out, n, H, maps, dv, dv_in, dv_out, lambda, norm, norm_scale, eps);
+    });
+}

@@ -64,6 +64,13 @@ _SIGNATURES = {
     "crane_pair_norm_mean": [I, P, P, I, L, P, P, I, L, P, P, F, P, I, I, P],
     "crane_delta_rule_prep": [I, P, P, I, L, I, P, P, P, P, P, I, I, I, I, F, F, P],
     "crane_delta_rule_scan": [I, P, P, I, L, I, P, P, P, P, I, P, P, F, P, P, P, I, I, I, I, I, P, P],
+    "crane_add_group_rmsnorm": [I, P, P, P, I, L, P, P, I, L, P, P, P, I, I, I, F, P],
+    "crane_poly_norm": [I, P, P, I, L, P, P, I, I, F, P],
+    "crane_scored_prep": [I, P, P, I, L, I, P, P, P, P, P, I, P, L, P, I, P, I, I, I, P, P, F, P, P, P, I, I, I, I,
+                          I, I, I, I, I, I, P, P, I, I, P, I, P, P],
+    "crane_head_finish": [I, P, P, P, P, I, I, I, I, I, I, F, I, F, F, P],
+    "crane_scored_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, I, I, P, I, I, I,
+                                    P, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -695,6 +702,70 @@ class Kernels:
             block_table.shape[1], k_pool.shape[0], page_size, q.shape[0], nq, nkv, d, dv, v_stride,
             int(window), float(scale), 1 if sink else 0, _ptr(out_cross), err.data_ptr(), self._stream(q)),
             "paged_attention_simt")
+
+    # ---- attention whose scores are worked on, and the block around it
+    def scored_attention_supports(self, d: int, nq: int, nkv: int, maps: int = 1) -> bool:
+        """Whether the warp-level kernels for worked-on scores take heads stored at ``d`` elements."""
+        return False
+
+    def add_group_rmsnorm(self, x, a: Optional[Act], f: Optional[Act], weight, groups: int, eps: float, out,
+                          rows=None) -> None:
+        """x += (a + f) (either may be None), then RMS norm in ``groups`` equal consecutive parts of the
+        row, times ``weight``.  With ``rows`` only those rows of x are read (and x is not written)."""
+        aw, ap, an, as_ = (None, None, 0, 0) if a is None else _split(a)
+        fw, fp, fn, fs = (None, None, 0, 0) if f is None else _split(f)
+        self._check(self.lib.crane_add_group_rmsnorm(
+            _dt(out.dtype), x.data_ptr(), aw, ap, an, as_, fw, fp, fn, fs, weight.data_ptr(), _ptr(rows),
+            out.data_ptr(), out.shape[0], x.shape[1], int(groups), float(eps), self._stream(x)), "add_group_rmsnorm")
+
+    def poly_norm(self, up: Act, coef, eps: float, out) -> None:
+        """out = a N(z) + b N(z^2) + c N(z^3) + e per row z of ``up``; ``coef`` float [4] = (a, b, c, e)."""
+        whole, parts, n_parts, stride = _split(up)
+        self._check(self.lib.crane_poly_norm(_dt(out.dtype), whole, parts, n_parts, stride, coef.data_ptr(),
+                                             out.data_ptr(), out.shape[0], out.shape[1], float(eps),
+                                             self._stream(out)), "poly_norm")
+
+    def scored_prep(self, proj: Act, cols, ctx, table, tails, conv_w, taps, page_size, q_norm_w, k_norm_w, eps, q_out,
+                    k_pool, v_pool, H, G, maps, dim, dv, dpad, cos, sin, rot_dims, gate_out, gate_col, err) -> None:
+        """Rows [q | k | v | gate] of a merged projection -> ``q_out`` [n, H, Dk], the token's rows in the
+        pools [pages, G, page_size, Dk / Dv] (zero-filled where wider than the heads), ``gate_out`` float
+        [n, H] = sigmoid(gate).  ``tails`` float [slots, taps - 1, channels] with ``conv_w`` [channels, taps]:
+        a causal convolution over time on every channel first, the slot's last inputs replaced afterwards.
+        A head holds ``maps`` maps of ``dim`` elements, map i stored at i * ``dpad``."""
+        whole, parts, n_parts, stride = _split(proj)
+        self._check(self.lib.crane_scored_prep(
+            _dt(q_out.dtype), whole, parts, n_parts, stride, int(cols), ctx.positions.data_ptr(),
+            ctx.tok_entry.data_ptr(), ctx.cu_q.data_ptr(), ctx.kv_len.data_ptr(), ctx.slots.data_ptr(),
+            tails.shape[0] if tails is not None else 0, _ptr(tails), tails.stride(0) if tails is not None else 0,
+            _ptr(conv_w), int(taps), table.data_ptr(), table.shape[1], k_pool.shape[0], page_size, _ptr(q_norm_w),
+            _ptr(k_norm_w), float(eps), q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), q_out.shape[0],
+            ctx.kv_len.shape[0], H, G, maps, dim, dv, k_pool.shape[3], dpad, v_pool.shape[3], _ptr(cos), _ptr(sin),
+            cos.shape[0] if cos is not None else 0, int(rot_dims) if cos is not None else 0, _ptr(gate_out),
+            int(gate_col), err.data_ptr(), self._stream(q_out)), "scored_prep")
+
+    def head_finish(self, a, tok_entry, gate, out, H, maps, dv, lam, norm: bool, norm_scale, eps) -> None:
+        """``a`` float [n, H, maps, dv_in] -> out [n, H, dv_out]: o = a1 - lam a2 for two maps, over the root of
+        its mean square times ``norm_scale`` (``norm``), times ``gate`` float [n, H] (or None)."""
+        n = out.shape[0]
+        self._check(self.lib.crane_head_finish(
+            _dt(out.dtype), a.data_ptr(), tok_entry.data_ptr(), _ptr(gate), out.data_ptr(), n, H, maps, dv,
+            a.shape[1] // (H * maps), out.shape[1] // H, float(lam), 1 if norm else 0, float(norm_scale), float(eps),
+            self._stream(out)), "head_finish")
+
+    def scored_attention_simt(self, q, out, k_pool, v_pool, positions, tok_entry, block_table, page_size, nq, nkv, d,
+                              dv, window, scale, err, softcap=0.0, chunk=0, sigmoid=False, head_bias=None, maps=1,
+                              d_row=None, d_map=None, out_f32=None) -> None:
+        """``paged_attention_simt`` with the scores worked on: squashed to softcap tanh(s / softcap), keys
+        seen within the query's block of ``chunk`` positions only, weights sigmoid(s + head_bias[h]) without
+        normalisation, ``maps`` maps of ``d`` elements per head (rows of ``d_row``, map i at i * ``d_map``),
+        results in float [n, nq, maps, dv] (``out_f32``) or in ``out``."""
+        d_row = int(d_row or maps * d)
+        self._check(self.lib.crane_scored_attention_simt(
+            _dt(q.dtype), q.data_ptr(), _ptr(out), k_pool.data_ptr(), v_pool.data_ptr(), positions.data_ptr(),
+            tok_entry.data_ptr(), block_table.data_ptr(), block_table.shape[1], k_pool.shape[0], page_size,
+            q.shape[0], nq, nkv, d, dv, v_pool.shape[3], int(window), float(scale), float(softcap), int(chunk),
+            1 if sigmoid else 0, _ptr(head_bias), int(maps), d_row, int(d_map or d), _ptr(out_f32), err.data_ptr(),
+            self._stream(q)), "scored_attention_simt")
 
     @staticmethod
     def decode_splits(entries: int, nkv: int, sms: int, cap: int = 64, max_keys: int = 1 << 30) -> int:

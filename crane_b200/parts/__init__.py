@@ -3,7 +3,7 @@ from .base import (CacheNeed, LayerCache, Part, Workspace, block_class, build_pa
                    register_block, register_part)
 from .runtime import DeviceFault, Runtime
 from . import (attention, block, delta_rule, embedding, feed_forward, latent_attention, norm, pair, position,   # register the parts
-               recurrent)
+               recurrent, scored_attention)
 from .model import DecoderModel, model_manifest
 
 __all__ = ["CacheNeed", "LayerCache", "Part", "Workspace", "block_class", "build_part",

@@ -13,6 +13,9 @@ token input joins the stream.
 is added once, and what the next layer reads is a weighted sum of all layer
 results so far.
 
+``parallel_shared_norm``: ONE norm that both sublayers read, h = norm1(x);
+x <- x + (mixer(h) + ffn(h)).
+
 ``hyper_connections``: R residual streams, all equal to the embedding output at the
 start; a sublayer reads u = sum_s in[s] x_s through its norm, and its result y joins
 all streams at once, x_t <- sum_s mix[s][t] x_s + out[t] y.  The model's last norm
@@ -97,6 +100,29 @@ class ParallelDepthAverageBlock:
         a = self.mixer.forward(h1, ctx, cache, rt)
         f = self.ffn.forward(h2, ctx, rt) if self.ffn is not None else None
         return BranchSum(a, f, self.combine)
+
+
+@register_block("parallel_shared_norm")
+class ParallelSharedNormBlock:
+    """h = norm1(x); x <- x + (mixer(h) + ffn(h)): the two sublayers read the same normed rows.  parts:
+    ``norm1``, ``mixer`` and, unless the layer has no feed-forward, ``ffn``.  The block hands its two
+    results on as a ``BranchSum``; the norm that reads the stream next adds them in its own kernel."""
+
+    def __init__(self, layer_spec):
+        p = layer_spec.parts
+        self.norm1 = build_part(p["norm1"])
+        self.mixer = build_part(p["mixer"])
+        self.ffn = build_part(p["ffn"]) if "ffn" in p else None
+
+    def parts(self):
+        return [q for q in (self.norm1, self.mixer, self.ffn) if q is not None]
+
+    def forward(self, x, pending, ctx, cache, rt):
+        h = self.norm1.forward(x, pending, rt)
+        # the mixer's result is read only after the feed-forward's products have run
+        a = self.mixer.forward(h, ctx, cache, rt, hold=self.ffn is not None)
+        f = self.ffn.forward(h, ctx, rt) if self.ffn is not None else None
+        return BranchSum(a, f)
 
 
 @register_part("entry", "pass_entry")

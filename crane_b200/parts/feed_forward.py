@@ -79,6 +79,37 @@ class XieluMlp(Part):
         return rt.linear(act, self.down, None, "ffn_down")
 
 
+@register_part("ffn", "poly_norm_mlp")
+class PolyNormMlp(Part):
+    """down(act(up(h))), no biases, act = PolyNorm with four learnt numbers (a, b, c, e):
+    a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N dividing a token's row by the root of
+    its mean square (+ eps), in 32-bit.  params: ``hidden_size``, ``intermediate_size``, ``eps``, ``names``
+    (up, down, act).  Tensors: up [I,H], down [H,I], act [4] (kept float)."""
+    kind = "ffn"
+    NAMES = {"up": "up", "down": "down", "act": "act"}
+
+    @classmethod
+    def manifest(cls, spec):
+        a, p = spec.params, spec.prefix
+        nm = dict(cls.NAMES, **(a.get("names") or {}))
+        h, i = a["hidden_size"], a["intermediate_size"]
+        return {p + nm["up"]: TensorSpec((i, h)), p + nm["down"]: TensorSpec((h, i)),
+                p + nm["act"]: TensorSpec((4,), "float32", "unit")}
+
+    def load(self, weights, rt):
+        a, p = self.params, self.prefix
+        nm = dict(self.NAMES, **(a.get("names") or {}))
+        self.inter, self.eps = int(a["intermediate_size"]), float(a["eps"])
+        self.up, self.down, self.coef = weights[p + nm["up"]], weights[p + nm["down"]], weights[p + nm["act"]]
+
+    def forward(self, h, ctx, rt):
+        up = rt.linear(h, self.up, None, "ffn_up")
+        act = rt.ws.get("ffn_act", h.shape[0], self.inter, rt.dtype)
+        rt.kernels.poly_norm(up, self.coef, self.eps, act)
+        rt.launches += 1
+        return rt.linear(act, self.down, None, "ffn_down")
+
+
 @register_part("ffn", "act_mlp")
 class ActMlp(Part):
     """down(act(up(h))), no biases.  params: ``hidden_size``, ``intermediate_size``, ``act``

@@ -43,6 +43,37 @@ class RMSNorm(Part):
         return out
 
 
+@register_part("norm", "group_rms_norm")
+class GroupRMSNorm(Part):
+    """RMS norm in groups: the row in ``groups`` equal consecutive parts, each over the root of its own
+    mean square (+ eps), the whole times w.  What is pending is added to the float stream first, in the
+    same kernel: a product's result, or the ``BranchSum`` of a block whose two sublayers read one norm
+    (their results are added to one another, then to the stream).  params: ``size``, ``eps``, ``groups``
+    (default 1), ``weight`` (tensor name behind the prefix, default "weight").  Tensor [size], kept float."""
+    kind = "norm"
+
+    @classmethod
+    def manifest(cls, spec):
+        return {spec.prefix + spec.params.get("weight", "weight"): TensorSpec((spec.params["size"],), "float32", "scale")}
+
+    def load(self, weights, rt):
+        self.weight = weights[self.prefix + self.params.get("weight", "weight")]
+        self.eps, self.size = float(self.params["eps"]), int(self.params["size"])
+        self.groups = int(self.params.get("groups") or 1)
+        if self.size % self.groups:
+            raise ValueError(f"{self.prefix}: {self.groups} groups do not divide a row of {self.size}")
+
+    def forward(self, x, pending, rt, rows=None, name="normed"):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = rt.ws.get(name, n, self.size, rt.dtype)
+        a, f = (pending.a, pending.f) if isinstance(pending, BranchSum) else (pending, None)
+        if isinstance(pending, BranchSum) and pending.combine is not None:
+            raise TypeError("group_rms_norm adds a block's two results as they are; it mixes no layer history")
+        rt.kernels.add_group_rmsnorm(x, a, f, self.weight, self.groups, self.eps, out, rows)
+        rt.launches += 1
+        return out
+
+
 def add_normed(x, delta, norm, rt, then=None, name="normed", raw_name=None):
     """x += norm(delta) (an ``rms_norm`` part applied to a sublayer's result before it joins the
     float stream) and, in the same kernel, ``then`` (another ``rms_norm`` part) of the new stream
