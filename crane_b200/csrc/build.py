@@ -7,7 +7,7 @@ sources when that is writable, otherwise to a per-user folder under the
 system's temporary directory, so a read-only checkout and an empty HOME both
 work.  There is no fallback: a failed build raises.
 
-The warp-level attention kernels are compiled per head size, two objects a
+The warp-level attention kernels are compiled per head size, three objects a
 size.  The CUDA library is linked for a set of head sizes: all eleven
 (``build_all``, what the build check and the tests use), or just the ones the
 models at hand have, so that a first call compiles what its model needs and no
@@ -35,15 +35,16 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
 BASE_SOURCES = ["elementwise.cu", "layer_parts.cu", "stream_parts.cu", "mixer_parts.cu", "hyper_parts.cu", "recurrent_parts.cu", "scored_parts.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu",
                 "latent_attention.cu", "latent_attention_mma.cu", "attention_decode.cu", "attention_prefill.cu",
-                "attention_prefill_tc.cu", "sampling.cu"]
-# the two files whose entry points pick a head size's launcher: compiled for the library's set of sizes
-DISPATCH_SOURCES = ("attention_decode.cu", "attention_prefill.cu")
+                "attention_prefill_tc.cu", "scored_attention.cu", "sampling.cu"]
+# the files whose entry points pick a head size's launcher: compiled for the library's set of sizes
+DISPATCH_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "scored_attention.cu")
 
 
 def kernel_sources(head_sizes: Sequence[int]) -> List[str]:
     sizes = sorted(set(head_sizes), reverse=True)          # the slowest to compile first
     return (BASE_SOURCES + [f"attention_decode.cu@CRANE_HEAD_SIZE={d}" for d in sizes]
-            + [f"attention_prefill.cu@CRANE_HEAD_SIZE={d}" for d in sizes])
+            + [f"attention_prefill.cu@CRANE_HEAD_SIZE={d}" for d in sizes]
+            + [f"scored_attention.cu@CRANE_HEAD_SIZE={d}" for d in sizes])
 
 
 KERNEL_SOURCES = kernel_sources(ATTENTION_HEAD_SIZES)

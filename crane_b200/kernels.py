@@ -8,6 +8,7 @@ raises.
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Union
 
@@ -71,6 +72,9 @@ _SIGNATURES = {
     "crane_head_finish": [I, P, P, P, P, I, I, I, I, I, I, F, I, F, F, P],
     "crane_scored_attention_simt": [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, I, I, P, I, I, I,
                                     P, P, P],
+    "crane_scored_attention_supports": [I, I, I, I],
+    "crane_scored_attention": [I, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, F, I, I, P, F, I,
+                               F, F, P, I, I, P, P],
     "crane_repetition_penalty": [P, L, I, I, P, I, P, P, P],
     "crane_sample": [P, L, I, I, P, P, P, P, P, P, P],
 }
@@ -704,9 +708,53 @@ class Kernels:
             "paged_attention_simt")
 
     # ---- attention whose scores are worked on, and the block around it
+    @dataclass
+    class ScoreMod:
+        """What happens to a score before it becomes a weight, and to a head's weighted sums afterwards
+        (the arguments of the warp-level kernels for worked-on scores)."""
+        softcap: float = 0.0
+        chunk: int = 0
+        sigmoid: bool = False
+        head_bias: Optional[torch.Tensor] = None     # float [heads]
+        maps: int = 1
+        lam: float = 0.0
+        head_norm: bool = False
+        norm_scale: float = 1.0
+        eps: float = 0.0
+        gate: Optional[torch.Tensor] = None          # float [rows, heads]
+        dv: int = 0                                   # the real width of a value row (0: the stored one)
+        compact: bool = False                         # out rows are [heads, dv] instead of [heads, stored]
+
     def scored_attention_supports(self, d: int, nq: int, nkv: int, maps: int = 1) -> bool:
         """Whether the warp-level kernels for worked-on scores take heads stored at ``d`` elements."""
-        return False
+        self.require_head_size(d)
+        return bool(self.lib.crane_scored_attention_supports(int(d), int(nq), int(nkv), int(maps)))
+
+    def _scored(self, decode, q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, table, page_size, tiles, nq,
+                nkv, d, window, scale, splits, skip_single, mod, err) -> None:
+        self._check(self.lib.crane_scored_attention(
+            1 if decode else 0, int(mod.maps), q.data_ptr(), out.data_ptr(), _ptr(part_o), _ptr(part_ml),
+            k_pool.data_ptr(), v_pool.data_ptr(), cu_q.data_ptr(), kv_len.data_ptr(), table.data_ptr(),
+            table.shape[1], k_pool.shape[0], page_size, kv_len.shape[0], int(tiles), nq, nkv, d, int(window),
+            float(scale), int(splits), 1 if skip_single else 0, float(mod.softcap), int(mod.chunk),
+            1 if mod.sigmoid else 0, _ptr(mod.head_bias), float(mod.lam), 1 if mod.head_norm else 0,
+            float(mod.norm_scale), float(mod.eps), _ptr(mod.gate), int(mod.dv or d), 1 if mod.compact else 0,
+            err.data_ptr(), self._stream(q)), "scored_attention")
+
+    def scored_prefill_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, table, page_size, tiles, nq, nkv, d,
+                                 window, scale, mod, err, skip_single: bool = False) -> None:
+        """bf16 attention with worked-on scores (``mod``) of q [rows, nq, d] over pools of head size d, for
+        every entry of the step (``skip_single``: but those of exactly one token).  ``tiles``: the query
+        tiles of 64 rows the entries have, or an upper bound."""
+        self._scored(False, q, out, None, None, k_pool, v_pool, cu_q, kv_len, table, page_size, tiles, nq, nkv, d,
+                     window, scale, 1, skip_single, mod, err)
+
+    def scored_decode_attention(self, q, out, k_pool, v_pool, cu_q, kv_len, table, page_size, nq, nkv, d, window,
+                                scale, splits, part_o, part_ml, mod, err) -> None:
+        """The same for the entries of exactly one token, the keys in ``splits`` slices; ``part_o`` float
+        [entries * nq * maps * splits, d] and ``part_ml`` [.., 2] hold the slices' sums for the merge."""
+        self._scored(True, q, out, part_o, part_ml, k_pool, v_pool, cu_q, kv_len, table, page_size, 0, nq, nkv, d,
+                     window, scale, splits, False, mod, err)
 
     def add_group_rmsnorm(self, x, a: Optional[Act], f: Optional[Act], weight, groups: int, eps: float, out,
                           rows=None) -> None:

@@ -215,8 +215,9 @@ def scored_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, sc
     scores: entries of one token through the split-KV kernel where that pays, the others through the
     kernel for portions.  Returns the launches."""
     n = q.shape[0]
-    decode = ctx.max_q_len == 1 and n == ctx.n_entries
-    singles = 0 if decode else getattr(ctx, "single_entries", 0)
+    split_kv = H // G <= 16                  # the query heads of a key/value head are the rows of one MMA tile
+    decode = split_kv and ctx.max_q_len == 1 and n == ctx.n_entries
+    singles = getattr(ctx, "single_entries", 0) if split_kv and not decode else 0
     launches = 0
     if decode or singles:
         if decode:
