@@ -120,9 +120,9 @@ struct PrepArgs {
     const int* kv_len;
     const int* slots;
     int n_slots;
-    const float* tails;             // [slots][taps - 1][C]: the convolutions' last inputs (null: no convolution)
+    const float* tails;             // [slots][taps - 1][C]: the convolutions' last inputs (taps > 1)
     long long slot_stride;
-    const float* conv_w;            // [C][taps]
+    const float* conv_w;            // [C][taps], or null: no convolution
     int taps;
     const int* block_table;
     int max_blocks, num_pages, page_size;
@@ -174,17 +174,20 @@ scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
     }
     const long long base = (long long)t * a.cols;
     float sq = 0.f, sk = 0.f;
-    if (a.tails != nullptr && a.taps > 1) {
+    if (a.conv_w != nullptr) {
         const int first = a.cu_q[e];
         const int i = t - first;                                      // the token's place in its portion
         const int start = a.kv_len[e] - (a.cu_q[e + 1] - first);      // tokens of the request before the step
-        const int slot = a.slots[e];
-        if (slot < 0 || slot >= a.n_slots) {
-            if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_SLOT_RANGE);
-            return;
-        }
-        const float* tail = a.tails + (long long)slot * a.slot_stride;
         const int taps = a.taps;
+        const float* tail = nullptr;                                  // (a single tap reads no earlier position)
+        if (taps > 1) {
+            const int slot = a.slots[e];
+            if (slot < 0 || slot >= a.n_slots) {
+                if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_SLOT_RANGE);
+                return;
+            }
+            tail = a.tails + (long long)slot * a.slot_stride;
+        }
         for (int c = threadIdx.x; c < C; c += blockDim.x) {
             float acc = 0.f;
             for (int j = 0; j < taps; ++j) {
@@ -351,7 +354,7 @@ CRANE_API int crane_scored_prep(int dtype, const void* proj, const float* proj_p
                                 cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     const int C = (H + G) * maps * dim + G * dv;
-    if (maps < 1 || dpad < dim || dk_store < maps * dpad || dv_store < dv || taps < 1 || rot_dims > dim ||
+    if (maps < 1 || dpad < dim || dk_store < maps * dpad || dv_store < dv || taps < 1 || rot_dims > dim || (conv_w != nullptr && taps > 1 && tails == nullptr) ||
         (size_t)C * sizeof(float) > 200 * 1024)
         return (int)cudaErrorInvalidValue;
     PrepArgs a;

@@ -35,7 +35,7 @@ from .base import CacheNeed, Part, build_part, query_tiles, register_part
 @register_part("mixer", "scored_attention")
 class ScoredAttention(Part):
     """params: ``hidden_size``, ``heads``, ``kv_heads``, ``dim`` (of one map of a query/key head), ``vdim``,
-    ``scale``, ``bias``, ``conv`` (taps; 0 or 1: none), ``qk_norm`` + ``norm_eps``, ``rotary_dim`` + ``position``
+    ``scale``, ``bias``, ``conv`` (taps; 0: none), ``qk_norm`` + ``norm_eps``, ``rotary_dim`` + ``position``
     (a PartSpec of kind position whose tables have rotary_dim / 2 columns), ``softcap`` (0: none), ``window``,
     ``chunk`` (0: none), ``weighting`` ("softmax" | "sigmoid"), ``head_bias`` (sigmoid: a number per head added
     to the score), ``maps`` (1 | 2), ``diff``, ``head_norm``, ``gate``, ``head_dim`` / ``map_stride`` (bfloat16:
@@ -66,7 +66,7 @@ class ScoredAttention(Part):
         if a.get("bias"):
             for n, c in (("q_bias", cq), ("k_bias", ck), ("v_bias", cv)):
                 out[p + nm[n]] = TensorSpec((c,), "float32", "offset")
-        if taps > 1:
+        if taps >= 1:
             for n, c in (("q_conv", cq), ("k_conv", ck), ("v_conv", cv)):
                 out[p + nm[n]] = TensorSpec((c, taps), "float32", "unit")
         if a.get("qk_norm"):
@@ -127,7 +127,7 @@ class ScoredAttention(Part):
                 bias.append(torch.zeros(H, dtype=torch.float32, device=bias[0].device))
             self.b_in = torch.cat(bias).contiguous()
         self.conv_w = None
-        if self.taps > 1:
+        if self.taps >= 1:
             self.conv_w = torch.cat([weights.pop(p + nm[n]) for n in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
         norm = bool(a.get("qk_norm"))
         self.q_norm = weights[p + nm["q_norm"]] if norm else None

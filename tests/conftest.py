@@ -36,6 +36,7 @@ def model_folders(tmp_path_factory):
     import tiny_radorax
     import tiny_mufevik
     import tiny_vodelix
+    import tiny_zudarax
     from crane_b200.weights.random_init import write_model_folder
     made = {}
 
@@ -43,7 +44,7 @@ def model_folders(tmp_path_factory):
         key = (name, dtype)
         if key not in made:
             d = tmp_path_factory.mktemp(f"{name}_{dtype}")
-            spec = next(t.TINY[name] for t in (tiny_configs, tiny_radorax, tiny_vodelix, tiny_mufevik) if name in t.TINY)
+            spec = next(t.TINY[name] for t in (tiny_configs, tiny_radorax, tiny_vodelix, tiny_mufevik, tiny_zudarax) if name in t.TINY)
             write_model_folder(str(d), spec["config"], spec["seed"], dtype, std=spec["std"],
                                norm_std=spec["norm_std"])
             made[key] = str(d)
