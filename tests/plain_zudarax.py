@@ -53,7 +53,7 @@ def load_folder(folder: str):
 
 # ------------------------------------------------------------------ small functions
 def sigmoid(z):
-    return 1.0 / (1.0 + np.exp(-z))
+    return 0.5 * (1.0 + np.tanh(0.5 * np.asarray(z, dtype=np.float64)))
 
 
 def unit_rms(x, eps):
@@ -250,8 +250,9 @@ def logits_all(cfg: dict, w: Dict[str, np.ndarray], tokens) -> np.ndarray:
 
 
 def greedy_generate(cfg: dict, w: Dict[str, np.ndarray], prompt: List[int], new_tokens: int) -> List[int]:
+    """The prompt and ``new_tokens`` more, each the largest logit's (ties to the lower index)."""
     logits, past = forward(cfg, w, prompt)
-    out, pos = [], len(prompt)
+    out, pos = list(prompt), len(prompt)
     for _ in range(new_tokens):
         tok = int(np.argmax(logits[-1]))
         out.append(tok)

@@ -235,5 +235,5 @@ def test_greedy_generation_continues_the_prompt():
     w = _weights(cfg, 5)
     prompt = [3, 9, 27, 1]
     out = pz.greedy_generate(cfg, w, prompt, 5)
-    assert len(out) == 5
-    assert out[1] == int(np.argmax(pz.logits_all(cfg, w, prompt + out[:1])[-1]))
+    assert len(out) == 9 and out[:4] == prompt
+    assert out[5] == int(np.argmax(pz.logits_all(cfg, w, out[:5])[-1]))
