@@ -143,10 +143,11 @@ def fill_cache(model, batch, context, seed=1):
     random keys and values, without running a prefill."""
     import torch
     g = torch.Generator(device="cuda:0"); g.manual_seed(seed)
-    for lc in model.runner.pools.layers:
-        if lc.k is not None:
-            lc.k.normal_(0.0, 1.0, generator=g)
-            lc.v.normal_(0.0, 1.0, generator=g)
+    for top in model.runner.pools.layers:
+        for lc in (top,) + tuple(top.parts):      # a mixer that keeps pages and a state has them as parts
+            if lc.k is not None:
+                lc.k.normal_(0.0, 1.0, generator=g)
+                lc.v.normal_(0.0, 1.0, generator=g)
     ids = list(range(1000, 1000 + batch))
     for rid in ids:
         model.runner.table.admit(rid)
@@ -1025,6 +1026,198 @@ def mufevik_workload(args, pk):
     return out
 
 
+def zudarax_config(like, layers):
+    """A Zudarax model with the width, layer count, head counts and vocabulary of the Hunyuan configuration
+    `like`: layers take turns between the three mixers (softmax attention behind convolutions of four taps
+    with half of each head rotated, squashed scores and blocks of 1,024 positions; differential attention with
+    two maps of 64 per head and values of 128; sigmoid attention behind the convolutions with YaRN), all with
+    heads stored at 128; norms in eight groups; the feed-forward's inner size one and a half times the
+    other's, which has three matrices where this one has two."""
+    h, heads, kv = like["hidden_size"], like["num_attention_heads"], like["num_key_value_heads"]
+    ff = like["intermediate_size"] * 3 // 2
+    soft = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
+            "rot": {"dims": 64, "base": 10000.0}, "softcap": 30.0, "mask": {"size": 1024}}
+    diff = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.5,
+            "rot": {"dims": 32, "base": 10000.0}}
+    sig = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
+           "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    kinds = (("attention", soft), ("attention_2", diff), ("attention_3", sig))
+    ls = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]
+    return {"architecture": "Zudarax", "vocab": like["vocab_size"], "width": h, "norm": {"eps": 1e-5, "groups": 8},
+            "layers": ls}
+
+
+def zudarax_kernel_table(zcfg, hcfg, pk, tokens, batch, context):
+    """Every kernel that only Zudarax runs beside the kernel of Hunyuan Dense (the engine's closest model:
+    attention layers only, a dense feed-forward) that does the like job, each alone on synthetic operands of
+    the two models' layer sizes (L2 flushed between repetitions), with the fraction of its roofline:
+    algorithmic bytes over the measured copy rate, or FLOPs over the measured bf16 rate, whichever takes
+    longer."""
+    from types import SimpleNamespace
+    import numpy as np
+    import torch
+    from crane_b200.kernels import get_kernels
+    K = get_kernels([128])
+    dev, bf, f32 = "cuda:0", torch.bfloat16, torch.float32
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    W, groups = zcfg["width"], zcfg["norm"]["groups"]
+    ffz, ffh = zcfg["layers"][0]["mlp"]["ff"], hcfg["intermediate_size"]
+    d, nq, nkv = hcfg["head_dim"], hcfg["num_attention_heads"], hcfg["num_key_value_heads"]
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, like, ms, nbytes, flops, like_ms=0, like_bytes=0, like_flops=0):
+        def frac(ms_, b, f):
+            return round(max(b / hbm, f / peak) / (ms_ * 1e-3), 4)
+        rows.append({"kernel": name, "ms": round(ms, 4), "frac": frac(ms, nbytes, flops), "like": like,
+                     "like_ms": round(like_ms, 4) if like_ms else None,
+                     "like_frac": frac(like_ms, like_bytes, like_flops) if like_ms else None})
+
+    T = tokens
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=dev, dtype=torch.float32).to(dt)
+    for n in (T, batch):
+        tag = "prompt" if n == T else f"{batch} tokens"
+        # two results join the stream and the next norm reads it / one result and the plain norm
+        x, a, f = rnd(n, W, dt=f32), rnd(n, W), rnd(n, W)
+        o1, w = torch.empty(n, W, device=dev, dtype=bf), rnd(W, dt=f32)
+        t_z = _median_ms(lambda: K.add_group_rmsnorm(x, a, f, w, groups, 1e-5, o1), flush=flush)
+        t_h = _median_ms(lambda: K.add_rmsnorm(x, a, w, 1e-5, o1), flush=flush)
+        add(f"add_group_rmsnorm ({tag})", "add_rmsnorm", t_z, n * W * (4 + 4 + 2 + 2 + 2), 0, t_h, n * W * (4 + 4 + 2 + 2), 0)
+        # the activation between the feed-forward's two products
+        up, act = rnd(n, ffz), torch.empty(n, ffz, device=dev, dtype=bf)
+        coef = rnd(4, dt=f32)
+        gu, act_h = rnd(n, 2 * ffh), torch.empty(n, ffh, device=dev, dtype=bf)
+        t_z = _median_ms(lambda: K.poly_norm(up, coef, 1e-5, act), flush=flush)
+        t_h = _median_ms(lambda: K.silu_mul(gu, act_h, False), flush=flush)
+        add(f"poly_norm ({tag})", "silu_mul", t_z, n * ffz * 4, 0, t_h, n * ffh * 6, 0)
+        del x, a, f, up, act, gu, act_h
+    ps = 64
+    kinds = {l["type"]: l["mixer"] for l in zcfg["layers"]}
+    for kind, n_req, q_len, kv in (("prompt", 1, T, T), (f"{batch} tokens", batch, 1, context)):
+        blocks = -(-kv // ps)
+        pages = n_req * blocks
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(n_req, blocks)
+        cu_d = torch.from_numpy(np.arange(n_req + 1, dtype=np.int32) * q_len).to(dev)
+        kv_d = torch.from_numpy(np.full(n_req, kv, dtype=np.int32)).to(dev)
+        n = n_req * q_len
+        pos = torch.from_numpy(np.concatenate([np.arange(kv - q_len, kv, dtype=np.int32)] * n_req)).to(dev)
+        ent = torch.from_numpy(np.repeat(np.arange(n_req, dtype=np.int32), q_len)).to(dev)
+        slots = torch.arange(n_req, dtype=torch.int32, device=dev)
+        ctx = SimpleNamespace(positions=pos, tok_entry=ent, cu_q=cu_d, kv_len=kv_d, slots=slots)
+        # the like kernels of Hunyuan Dense
+        k_pool, v_pool = rnd(pages, nkv, ps, d), rnd(pages, nkv, ps, d)
+        qkv_h = rnd(n, (nq + 2 * nkv) * d)
+        qh, oh = rnd(n, nq * d), torch.empty(n, nq * d, device=dev, dtype=bf)
+        cos, sin = torch.rand(kv, d // 2, device=dev), torch.rand(kv, d // 2, device=dev)
+        nw = rnd(d, dt=f32)
+        t_rope = _median_ms(lambda: K.rope_norm_cache(qkv_h, (nq + 2 * nkv) * d, bf, pos, ent, table, cos, sin, nw, nw, 1e-5,
+                                                      qh, k_pool, v_pool, ps, nq, nkv, d, True, True, err), flush=flush)
+        b_rope = n * (nq + 2 * nkv) * d * 2 * 2
+        pairs = T * T / 2
+        if q_len > 1:
+            tiles64 = -(-T // 64)
+            t_like = _median_ms(lambda: K.paged_prefill_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, tiles64, nq,
+                                                                  nkv, d, 0, d ** -0.5, err), flush=flush)
+            t_tc = _median_ms(lambda: K.prefill_attention_tc(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, -(-T // 128),
+                                                             nq, nkv, d, 0, d ** -0.5, err), flush=flush)
+            add("(the like kernel beside the tcgen05 one)", "prefill_attn_tc (tcgen05)", t_like, 0, pairs * nq * 4 * d,
+                t_tc, 0, pairs * nq * 4 * d)
+        else:
+            sp = K.decode_splits(n_req, nkv, 148, 64, max_keys=kv)
+            po, pml = torch.empty(n_req * nq * sp, d, device=dev), torch.empty(n_req * nq * sp, 2, device=dev)
+            t_like = _median_ms(lambda: K.paged_decode_attention(qh, oh, k_pool, v_pool, cu_d, kv_d, table, ps, nq, nkv, d, 0,
+                                                                 d ** -0.5, sp, po, pml, err), flush=flush)
+        kvb = n_req * kv * nkv * d * 2 * 2
+        for name, m in kinds.items():
+            H, G, dim, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            maps = 2 if name == "attention_2" else 1
+            taps = m.get("conv", 0)
+            D, dpad = 128, 128 // maps
+            cq, ck, cv = H * maps * dim, G * maps * dim, G * vd
+            C = cq + ck + cv
+            cols = C + (H if maps == 2 else 0)
+            proj = rnd(n, cols)
+            conv_w = rnd(C, taps, dt=f32) if taps else None
+            tails = torch.zeros(n_req, (taps - 1) * C, device=dev) if taps > 1 else None
+            qn, kn = (rnd(cq, dt=f32), rnd(ck, dt=f32)) if name == "attention" else (None, None)
+            rot = m["rot"]["dims"]
+            cz, sz = torch.rand(kv, rot // 2, device=dev), torch.rand(kv, rot // 2, device=dev)
+            q = torch.empty(n, H * D, device=dev, dtype=bf)
+            gate = torch.empty(n, H, device=dev) if maps == 2 else None
+            t_p = _median_ms(lambda: K.scored_prep(proj, cols, ctx, table, tails, conv_w, max(taps, 1), ps, qn, kn, 1e-5, q,
+                                                   k_pool, v_pool, H, G, maps, dim, vd, dpad, cz, sz, rot, gate, C, err),
+                             flush=flush)
+            add(f"scored_prep, {name} ({kind})", "rope_norm_cache", t_p, n * C * 2 * 2 + (n * C * 2 * (taps - 1) if taps and
+                q_len == 1 else 0), 0, t_rope, b_rope, 0)
+            finish = maps == 2
+            mod = K.ScoreMod(softcap=m.get("softcap", 0.0), chunk=(m.get("mask") or {}).get("size", 0),
+                             sigmoid=name == "attention_3", head_bias=rnd(H, dt=f32) if name == "attention_3" else None,
+                             maps=maps, lam=0.4, head_norm=finish, norm_scale=0.5, eps=1e-5, gate=gate, dv=vd, compact=finish)
+            o = torch.empty(n, H * (vd if finish else D), device=dev, dtype=bf)
+            q.copy_(rnd(n, H * D))
+            if q_len > 1:
+                t_a = _median_ms(lambda: K.scored_prefill_attention(q, o, k_pool, v_pool, cu_d, kv_d, table, ps, -(-T // 64),
+                                                                    H, G, D, 0, m["scale"], mod, err), flush=flush)
+                blk = mod.chunk or T
+                seen = T * min(blk, T) / 2 if blk < T else pairs          # (query, key) pairs that are visible
+                add(f"scored_prefill_attn, {name} (prompt)", "paged_prefill_attn (warp-level MMA)", t_a, 0,
+                    seen * H * (2 * D + 2 * D * maps), t_like, 0,
+                    pairs * nq * 4 * d)
+            else:
+                sp = max(1, min(32, (2 * 148) // max(1, n_req * G)))
+                po = torch.empty(n_req * H * maps * sp, D, device=dev)
+                pml = torch.empty(n_req * H * maps * sp, 2, device=dev)
+                t_a = _median_ms(lambda: K.scored_decode_attention(q, o, k_pool, v_pool, cu_d, kv_d, table, ps, H, G, D, 0,
+                                                                   m["scale"], sp, po, pml, mod, err), flush=flush)
+                blk = mod.chunk or kv
+                read = min(kv, (kv - 1) % blk + 1)                        # keys a token at position kv - 1 sees
+                add(f"scored_decode_attn + merge, {name} ({kind})", "paged_decode_attn", t_a, n_req * read * G * D * 2 * 2, 0,
+                    t_like, kvb, 0)
+            del proj, q, o
+        del k_pool, v_pool, qkv_h, qh, oh
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    return rows
+
+
+def zudarax_workload(args, pk):
+    """Prefill and decode throughput of Zudarax at the layer sizes of --sizes beside Hunyuan Dense (the
+    engine's closest model) at the same width, heads, layers and vocabulary, random weights, and the
+    kernels of the two side by side."""
+    import gc
+    import torch
+    hcfg = dict(MODEL)
+    hcfg.update(OTHER_SIZES.get(args.sizes, {}))
+    layers = args.layers or 12
+    hcfg["num_hidden_layers"] = layers
+    zcfg = zudarax_config(hcfg, layers)
+    page, pt = 64, args.prefill_tokens
+    out = {"workload": "zudarax", "sizes": args.sizes, "layers": layers, "batch": args.batch,
+           "context": args.context, "prefill_tokens": pt, "dtype": "bf16", "data": "synthetic", "models": {}}
+    for name, cfg in (("zudarax", zcfg), ("hunyuan_dense", hcfg)):
+        opts = dict(page_size=page, num_pages=(args.batch * (args.context + args.steps + args.warmup + 64) + pt) // page + 64,
+                    max_concurrent=max(64, args.batch), max_seq_len=max(args.context, pt) + 1024,
+                    max_batched_tokens=max(2048, pt), chunk_size=max(2048, pt))
+        vocab = cfg.get("vocab") or cfg["vocab_size"]
+        model = build_model(cfg, opts)
+        pms = time_prefill(model, pt, vocab, reps=3)
+        ids = fill_cache(model, args.batch, args.context)
+        dms, launches = time_decode(model, ids, args.steps, args.warmup, vocab)
+        weights = sum(t.numel() * t.element_size() for t in _model_tensors(model))
+        out["models"][name] = {"prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(pt * 1000.0 / pms, 1),
+                               "decode_ms_per_step": round(dms, 4),
+                               "decode_tokens_per_s": round(args.batch * 1000.0 / dms, 1),
+                               "launches_per_decode_step": launches, "weight_bytes": weights,
+                               "layer_runs": len(model.runner.spec.schedule)}
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+    out["kernels"] = zudarax_kernel_table(zcfg, hcfg, pk, pt, args.batch, args.context)
+    out["peaks"] = pk
+    return out
+
+
 def _model_tensors(model):
     seen, out = set(), []
     parts = [model.runner.model.embed, model.runner.model.final_norm, model.runner.model.head]
@@ -1064,7 +1257,7 @@ def main():
                     help="layer sizes: Hunyuan 1.8B (the default, the headline configuration), 4B or 7B")
     ap.add_argument("--prefill-chunk", type=int, default=0,
                     help="with --only-prefill: also time the prompt in portions of this many tokens, a step each")
-    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax", "vodelix", "mufevik"],
+    ap.add_argument("--workload", default="", choices=["", "serve", "mixed-step", "radorax", "vodelix", "mufevik", "zudarax"],
                     help="serve: a mix of requests through the scheduler; mixed-step: decoded tokens beside "
                          "one prompt portion in one step; radorax: prefill and decode of Radorax beside Hunyuan "
                          "Dense at equal layer sizes, and their kernels side by side; vodelix: the same for Vodelix; "
@@ -1088,6 +1281,9 @@ def main():
         return 2
     args.warmup = max(args.warmup, 3)
 
+    if args.workload == "zudarax":
+        print(json.dumps(zudarax_workload(args, peaks())))
+        return 0
     if args.workload == "mufevik":
         print(json.dumps(mufevik_workload(args, peaks())))
         return

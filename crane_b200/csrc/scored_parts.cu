@@ -67,9 +67,12 @@ add_group_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> a, int has_a, GemmOut
 }
 
 // ------------------------------------------------------ PolyNorm
-template <typename T>
-__global__ void __launch_bounds__(256)
+// The row is read once (partial sums are added up once) and kept in shared memory between the pass that
+// forms the three mean squares and the pass that writes; CACHED false: rows too long for that are read twice.
+template <typename T, bool CACHED>
+__global__ void __launch_bounds__(1024)
 poly_norm_kernel(GemmOut<T> up, const float* __restrict__ coef, T* __restrict__ out, int F, float eps) {
+    extern __shared__ float zrow[];                   // [F] when CACHED
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -78,6 +81,7 @@ poly_norm_kernel(GemmOut<T> up, const float* __restrict__ coef, T* __restrict__ 
     if ((F & 1) == 0) {
         for (int c = 2 * threadIdx.x; c < F; c += 2 * blockDim.x) {
             const float2 z = up.load2(base + c);
+            if (CACHED) *(float2*)(zrow + c) = z;
             const float a = z.x * z.x, b = z.y * z.y;
             s2 += a + b;
             s4 += a * a + b * b;
@@ -86,6 +90,7 @@ poly_norm_kernel(GemmOut<T> up, const float* __restrict__ coef, T* __restrict__ 
     } else {
         for (int c = threadIdx.x; c < F; c += blockDim.x) {
             const float z = up.load(base + c), a = z * z;
+            if (CACHED) zrow[c] = z;
             s2 += a;
             s4 += a * a;
             s6 += a * a * a;
@@ -97,16 +102,78 @@ poly_norm_kernel(GemmOut<T> up, const float* __restrict__ coef, T* __restrict__ 
     const float inv = 1.f / (float)F;
     const float r1 = coef[0] * rsqrtf(s2 * inv + eps), r2 = coef[1] * rsqrtf(s4 * inv + eps),
                 r3 = coef[2] * rsqrtf(s6 * inv + eps), e = coef[3];
+    // each thread reads back what it wrote itself
     if ((F & 1) == 0) {
         for (int c = 2 * threadIdx.x; c < F; c += 2 * blockDim.x) {
-            const float2 z = up.load2(base + c);
+            const float2 z = CACHED ? *(const float2*)(zrow + c) : up.load2(base + c);
             st2(out + base + c, fmaf(z.x, fmaf(z.x, fmaf(z.x, r3, r2), r1), e),
                 fmaf(z.y, fmaf(z.y, fmaf(z.y, r3, r2), r1), e));
         }
     } else {
         for (int c = threadIdx.x; c < F; c += blockDim.x) {
-            const float z = up.load(base + c);
+            const float z = CACHED ? zrow[c] : up.load(base + c);
             out[base + c] = from_f32<T>(fmaf(z, fmaf(z, fmaf(z, r3, r2), r1), e));
+        }
+    }
+}
+
+// Many rows of bf16 that come whole: every thread keeps its share of the row in registers, 16 bytes a load
+// (NV loads a thread, all in flight together), one round of block sums for the three mean squares.
+template <int NV>
+__global__ void __launch_bounds__(256)
+poly_norm_bf16_rows_kernel(const __nv_bfloat16* __restrict__ up, const float* __restrict__ coef,
+                           __nv_bfloat16* __restrict__ out, int F, float eps) {
+    __shared__ float red[3][8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint4* src = (const uint4*)(up + (long long)blockIdx.x * F);
+    uint4* dst = (uint4*)(out + (long long)blockIdx.x * F);
+    const int nvec = F >> 3;
+    uint4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int idx = threadIdx.x + k * 256;
+        v[k] = idx < nvec ? src[idx] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const __nv_bfloat162* h = (const __nv_bfloat162*)&v[k];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 z = __bfloat1622float2(h[i]);
+            const float a = z.x * z.x, b = z.y * z.y;
+            s2 += a + b;
+            s4 += a * a + b * b;
+            s6 += a * a * a + b * b * b;
+        }
+    }
+    s2 = warp_sum(s2);
+    s4 = warp_sum(s4);
+    s6 = warp_sum(s6);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { red[0][warp] = s2; red[1][warp] = s4; red[2][warp] = s6; }
+    __syncthreads();
+    s2 = s4 = s6 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { s2 += red[0][w]; s4 += red[1][w]; s6 += red[2][w]; }
+    const float inv = 1.f / (float)F;
+    const float r1 = coef[0] * rsqrtf(s2 * inv + eps), r2 = coef[1] * rsqrtf(s4 * inv + eps),
+                r3 = coef[2] * rsqrtf(s6 * inv + eps), e = coef[3];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int idx = threadIdx.x + k * 256;
+        if (idx < nvec) {
+            uint4 o;
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&v[k];
+            __nv_bfloat162* q = (__nv_bfloat162*)&o;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 z = __bfloat1622float2(h[i]);
+                q[i] = __floats2bfloat162_rn(fmaf(z.x, fmaf(z.x, fmaf(z.x, r3, r2), r1), e),
+                                             fmaf(z.y, fmaf(z.y, fmaf(z.y, r3, r2), r1), e));
+            }
+            dst[idx] = o;
         }
     }
 }
@@ -155,8 +222,11 @@ __device__ __forceinline__ float prep_element(const float* sm, const float* nw, 
     return v;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256)
+// TAPS: the convolution's taps when they are 2, 3 or 4 (the loads of a channel's taps are then in flight
+// together), 0: any number, or no convolution.  VEC: two neighbouring channels a thread (every width even,
+// the rotated half even): loads and stores of pairs.
+template <typename T, int TAPS, bool VEC>
+__global__ void __launch_bounds__(1024)
 scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
     extern __shared__ float sm[];                     // [C] the token's q, k, v after the convolution
     __shared__ float scratch[32];
@@ -172,13 +242,14 @@ scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
         if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_POSITION_RANGE);
         return;
     }
+    constexpr int W = VEC ? 2 : 1;
     const long long base = (long long)t * a.cols;
     float sq = 0.f, sk = 0.f;
     if (a.conv_w != nullptr) {
         const int first = a.cu_q[e];
         const int i = t - first;                                      // the token's place in its portion
         const int start = a.kv_len[e] - (a.cu_q[e + 1] - first);      // tokens of the request before the step
-        const int taps = a.taps;
+        const int taps = TAPS ? TAPS : a.taps;
         const float* tail = nullptr;                                  // (a single tap reads no earlier position)
         if (taps > 1) {
             const int slot = a.slots[e];
@@ -188,25 +259,38 @@ scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
             }
             tail = a.tails + (long long)slot * a.slot_stride;
         }
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
-            float acc = 0.f;
-            for (int j = 0; j < taps; ++j) {
+        for (int c = W * threadIdx.x; c < C; c += W * blockDim.x) {
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < (TAPS ? TAPS : taps); ++j) {
                 const int back = taps - 1 - j;
-                float u = 0.f;
-                if (i - back >= 0) u = proj.load(base - (long long)back * a.cols + c);
-                else if (start + i - back >= 0) u = tail[(long long)(taps - 1 + i - back) * C + c];
-                acc = fmaf(a.conv_w[(long long)c * taps + j], u, acc);
+                float u0 = 0.f, u1 = 0.f;
+                if (i - back >= 0) {
+                    if (VEC) { const float2 u = proj.load2(base - (long long)back * a.cols + c); u0 = u.x; u1 = u.y; }
+                    else u0 = proj.load(base - (long long)back * a.cols + c);
+                } else if (start + i - back >= 0) {
+                    const float* p = tail + (long long)(taps - 1 + i - back) * C + c;
+                    if (VEC) { const float2 u = *(const float2*)p; u0 = u.x; u1 = u.y; }
+                    else u0 = *p;
+                }
+                acc0 = fmaf(a.conv_w[(long long)c * taps + j], u0, acc0);
+                if (VEC) acc1 = fmaf(a.conv_w[(long long)(c + 1) * taps + j], u1, acc1);
             }
-            sm[c] = acc;
-            if (c < Cq) sq = fmaf(acc, acc, sq);
-            else if (c < Cq + Ck) sk = fmaf(acc, acc, sk);
+            sm[c] = acc0;
+            if (VEC) sm[c + 1] = acc1;
+            const float ss = VEC ? fmaf(acc0, acc0, acc1 * acc1) : acc0 * acc0;
+            if (c < Cq) sq += ss;
+            else if (c < Cq + Ck) sk += ss;
         }
     } else {
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
-            const float v = proj.load(base + c);
-            sm[c] = v;
-            if (c < Cq) sq = fmaf(v, v, sq);
-            else if (c < Cq + Ck) sk = fmaf(v, v, sk);
+        for (int c = W * threadIdx.x; c < C; c += W * blockDim.x) {
+            float v0, v1 = 0.f;
+            if (VEC) { const float2 u = proj.load2(base + c); v0 = u.x; v1 = u.y; sm[c + 1] = v1; }
+            else v0 = proj.load(base + c);
+            sm[c] = v0;
+            const float ss = fmaf(v0, v0, v1 * v1);
+            if (c < Cq) sq += ss;
+            else if (c < Cq + Ck) sk += ss;
         }
     }
     float rq = 1.f, rk = 1.f;
@@ -215,36 +299,52 @@ scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
     __syncthreads();
     const float* ct = a.cos_tab + (long long)pos * half;
     const float* sn = a.sin_tab + (long long)pos * half;
-    T* q_out = (T*)a.q_out + (long long)t * a.H * a.dk_store;
-    for (int c = threadIdx.x; c < a.H * a.dk_store; c += blockDim.x) {
-        const int h = c / a.dk_store, r = c % a.dk_store, mp = r / a.dpad, i = r % a.dpad;
-        float v = 0.f;
-        if (mp < a.maps && i < a.dim) v = prep_element(sm, a.qw, rq, (h * a.maps + mp) * a.dim, i, half, ct, sn);
-        q_out[c] = from_f32<T>(v);
-    }
     if (a.gate_out != nullptr)
         for (int h = threadIdx.x; h < a.H; h += blockDim.x)
             a.gate_out[(long long)t * a.H + h] = 1.f / (1.f + expf(-proj.load(base + a.gate_col + h)));
     const int blk = pos / a.page_size;
     const int page = (pos >= 0 && blk < a.max_blocks) ? a.block_table[(long long)e * a.max_blocks + blk] : -1;
-    if (page < 0 || page >= a.num_pages) {
-        if (threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_PAGE_RANGE);
-        return;
-    }
-    const int place = pos % a.page_size;
-    T* k_pool = (T*)a.k_pool;
-    T* v_pool = (T*)a.v_pool;
-    for (int c = threadIdx.x; c < a.G * a.dk_store; c += blockDim.x) {
-        const int g = c / a.dk_store, r = c % a.dk_store, mp = r / a.dpad, i = r % a.dpad;
-        float v = 0.f;
-        if (mp < a.maps && i < a.dim)
-            v = prep_element(sm + Cq, a.kw, rk, (g * a.maps + mp) * a.dim, i, half, ct, sn);
-        k_pool[(((long long)page * a.G + g) * a.page_size + place) * a.dk_store + r] = from_f32<T>(v);
-    }
-    for (int c = threadIdx.x; c < a.G * a.dv_store; c += blockDim.x) {
-        const int g = c / a.dv_store, i = c % a.dv_store;
-        const float v = i < a.dv ? sm[Cq + Ck + g * a.dv + i] : 0.f;
-        v_pool[(((long long)page * a.G + g) * a.page_size + place) * a.dv_store + i] = from_f32<T>(v);
+    const bool page_ok = page >= 0 && page < a.num_pages;
+    if (!page_ok && threadIdx.x == 0) atomicOr(a.err, CRANE_ERR_PAGE_RANGE);
+    const long long place = ((long long)page * a.G) * a.page_size + pos % a.page_size;   // of key/value head 0
+    // a warp per stored head: H of queries, then G of keys, then G of values
+    const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int u = threadIdx.x >> 5; u < a.H + 2 * a.G; u += nwarps) {
+        if (u >= a.H && !page_ok) break;
+        if (u < a.H + a.G) {
+            const bool is_q = u < a.H;
+            const int hd = is_q ? u : u - a.H;
+            T* dst = is_q ? (T*)a.q_out + ((long long)t * a.H + hd) * a.dk_store
+                          : (T*)a.k_pool + (place + (long long)hd * a.page_size) * a.dk_store;
+            const float* src = is_q ? sm : sm + Cq;
+            const float* nw = is_q ? a.qw : a.kw;
+            const float rn = is_q ? rq : rk;
+            for (int mp = 0; mp < a.maps; ++mp) {
+                const int ch0 = (hd * a.maps + mp) * a.dim;
+                for (int i = W * lane; i < a.dpad; i += W * 32) {
+                    float v0 = 0.f, v1 = 0.f;
+                    if (i < a.dim) {
+                        v0 = prep_element(src, nw, rn, ch0, i, half, ct, sn);
+                        if (VEC) v1 = prep_element(src, nw, rn, ch0, i + 1, half, ct, sn);
+                    }
+                    if (VEC) st2(dst + mp * a.dpad + i, v0, v1);
+                    else dst[mp * a.dpad + i] = from_f32<T>(v0);
+                }
+            }
+            for (int i = a.maps * a.dpad + W * lane; i < a.dk_store; i += W * 32) {
+                if (VEC) st2(dst + i, 0.f, 0.f);
+                else dst[i] = from_f32<T>(0.f);
+            }
+        } else {
+            const int g = u - a.H - a.G;
+            T* dst = (T*)a.v_pool + (place + (long long)g * a.page_size) * a.dv_store;
+            const float* src = sm + Cq + Ck + g * a.dv;
+            for (int i = W * lane; i < a.dv_store; i += W * 32) {
+                const float v0 = i < a.dv ? src[i] : 0.f;
+                if (VEC) st2(dst + i, v0, i + 1 < a.dv ? src[i + 1] : 0.f);
+                else dst[i] = from_f32<T>(v0);
+            }
+        }
     }
 }
 
@@ -335,9 +435,33 @@ CRANE_API int crane_add_group_rmsnorm(int dtype, float* x, const void* a, const 
 CRANE_API int crane_poly_norm(int dtype, const void* up, const float* up_parts, int n_parts, long long part_stride,
                               const float* coef, void* out, int n_rows, int F, float eps, cudaStream_t st) {
     if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)F * sizeof(float);
+    const bool cached = smem <= 96 * 1024;
+    // few rows: more threads a row (what bounds them is the chain of loads a thread waits for)
+    const int threads = n_rows <= 64 ? 1024 : 256;
+    if (dtype == 1 && up != nullptr && n_rows > 64 && F % 8 == 0 && F <= 16384 && ((uintptr_t)up & 15) == 0 &&
+        ((uintptr_t)out & 15) == 0) {
+        const __nv_bfloat16* u = (const __nv_bfloat16*)up;
+        __nv_bfloat16* o = (__nv_bfloat16*)out;
+        if (F <= 4096) return crane_launch(poly_norm_bf16_rows_kernel<2>, dim3(n_rows), dim3(256), 0, st, u, coef, o, F, eps);
+        if (F <= 8192) return crane_launch(poly_norm_bf16_rows_kernel<4>, dim3(n_rows), dim3(256), 0, st, u, coef, o, F, eps);
+        if (F <= 12288) return crane_launch(poly_norm_bf16_rows_kernel<6>, dim3(n_rows), dim3(256), 0, st, u, coef, o, F, eps);
+        return crane_launch(poly_norm_bf16_rows_kernel<8>, dim3(n_rows), dim3(256), 0, st, u, coef, o, F, eps);
+    }
     DISPATCH_T(dtype, {
         GemmOut<T> g{(const T*)up, up_parts, n_parts, part_stride};
-        return crane_launch(poly_norm_kernel<T>, dim3(n_rows), dim3(256), 0, st, g, coef, (T*)out, F, eps);
+        if (!cached)
+            return crane_launch(poly_norm_kernel<T, false>, dim3(n_rows), dim3(threads), 0, st, g, coef, (T*)out, F, eps);
+        auto kern = poly_norm_kernel<T, true>;
+        if (smem > 48 * 1024) {
+            static size_t configured = 0;
+            if (configured < smem) {
+                if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                    return (int)cudaGetLastError();
+                configured = smem;
+            }
+        }
+        return crane_launch(kern, dim3(n_rows), dim3(threads), smem, st, g, coef, (T*)out, F, eps);
     });
 }
 
@@ -369,16 +493,22 @@ CRANE_API int crane_scored_prep(int dtype, const void* proj, const float* proj_p
     const size_t smem = (size_t)C * sizeof(float);
     DISPATCH_T(dtype, {
         GemmOut<T> g{(const T*)proj, proj_parts, n_parts, part_stride};
-        auto kern = scored_prep_kernel<T>;
+        // pairs of channels where every width is even and a rotated half is too; the taps known at compile
+        // time where they are few
+        const bool vec = !(dim & 1) && !(dv & 1) && !(dpad & 1) && !(dk_store & 1) && !(dv_store & 1) && !(cols & 1) &&
+                         !(a.rot_dims & 3) && !(slot_stride & 1);
+        const int known = (conv_w != nullptr && taps >= 2 && taps <= 4) ? taps : 0;
+        void (*kern)(GemmOut<T>, const PrepArgs) = nullptr;
+        if (vec) kern = known == 2 ? scored_prep_kernel<T, 2, true> : known == 3 ? scored_prep_kernel<T, 3, true>
+                      : known == 4 ? scored_prep_kernel<T, 4, true> : scored_prep_kernel<T, 0, true>;
+        else kern = known == 2 ? scored_prep_kernel<T, 2, false> : known == 3 ? scored_prep_kernel<T, 3, false>
+                  : known == 4 ? scored_prep_kernel<T, 4, false> : scored_prep_kernel<T, 0, false>;
         if (smem > 48 * 1024) {
-            static size_t configured = 0;
-            if (configured < smem) {
-                if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                    return (int)cudaGetLastError();
-                configured = smem;
-            }
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                return (int)cudaGetLastError();
         }
-        int rc = crane_launch(kern, dim3(n_tokens), dim3(256), smem, st, g, a);
+        // few tokens: more threads a token (what bounds them is the chain of loads a thread waits for)
+        int rc = crane_launch(kern, dim3(n_tokens), dim3(n_tokens <= 64 ? 1024 : 256), smem, st, g, a);
         if (rc != 0 || taps <= 1 || tails == nullptr) return rc;
         return crane_launch(conv_tail_update_kernel<T>, dim3((C + 127) / 128, n_entries), dim3(128), 0, st, g, cols,
                             cu_q, kv_len, slots, n_slots, tails, slot_stride, taps, C);

@@ -166,8 +166,14 @@ class ModelRunner:
         # steps with prompt portions are, to a shape of their own.
         # (State that only the embedding keeps, one token per request that its kernel reads and replaces
         # for entries with rows alone, bears the bucket's padding as well.)
+        # (So does a mixer that says so, ``decode_bucket_safe``: its kernels leave rows of no entry alone and
+        # touch no slot for an entry without rows also when every entry has one token.)
         mixer_state = any(f.kind == "state" for n in self.model.cache_needs()[:len(self.spec.schedule)]
                           for f in n.flat())
+        if mixer_state:
+            keepers = [self.model.blocks[s.layer].mixer for s in self.spec.schedule if s.cache_of is None]
+            mixer_state = not all(getattr(mx, "decode_bucket_safe", False) for mx in keepers
+                                  if any(f.kind == "state" for f in mx.cache_need().flat()))
         self._pad_with_copies = not mixer_state
         self.graph_replays = 0
         self.graph_captures = 0                    # steps that ran kernel by kernel and were recorded for their shape

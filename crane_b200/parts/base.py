@@ -133,6 +133,11 @@ class Part:
     # Steps are only ever padded with such rows and entries, never with copies of an entry (a copy
     # would advance its request's state twice).
     state_graph_safe = False
+    # For a mixer with ``state_graph_safe``: True says that it bears the padding of a decode step's
+    # batch-size bucket as well (every entry has one token, the step is filled up to the bucket with rows
+    # of no entry and entries without rows, ``ctx.max_q_len == 1``), so that its model's decode steps take
+    # the buckets as a model without state does, instead of a shape of 64 rows.
+    decode_bucket_safe = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

@@ -46,6 +46,7 @@ class ScoredAttention(Part):
     k.norm; with ``head_bias`` pb [H]; with ``maps`` 2 lq1, lk1, lq2, lk2 [dim]; with ``gate`` g [H, hidden]."""
     kind = "mixer"
     state_graph_safe = True
+    decode_bucket_safe = True
     NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b",
              "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "q_norm": "q.norm", "k_norm": "k.norm",
              "head_bias": "pb", "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2", "gate": "g"}

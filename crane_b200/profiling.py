@@ -6,6 +6,9 @@ against the roofline: the command that profiles are taken with.
     python -m crane_b200.profiling decode-attention --batch 8 --context 8192
     python -m crane_b200.profiling prefill-attention --tokens 2048
     python -m crane_b200.profiling rmsnorm --rows 2048 --hidden 2048
+    python -m crane_b200.profiling scored-attention --weights softmax|sigmoid|two-maps --tokens 2048
+    python -m crane_b200.profiling scored-attention --weights sigmoid --batch 8 --context 8192    (single tokens)
+    python -m crane_b200.profiling scored-prep --tokens 2048 --taps 4 [--two-maps] [--norm]
 
 Times are CUDA-event times over --reps launches after --warmup; operands are
 re-used between launches, so keep them larger than the 126 MB L2 where the
@@ -190,6 +193,92 @@ def rmsnorm(a):
     _report(f"add_rmsnorm {a.rows}x{a.hidden}", t, a.rows * a.hidden * (4 + 2 + 4 + 2), 0.0, {"sets": a.sets})
 
 
+def _scored_setup(a, n_req, q_len, kv):
+    """Block tables, step metadata and pools of ``n_req`` requests with ``kv`` cached positions each, the last
+    ``q_len`` of them in the step."""
+    from types import SimpleNamespace
+    import numpy as np
+    ps, G, D = a.page_size, a.kv_heads, a.head_dim
+    blocks = -(-kv // ps)
+    table = torch.arange(n_req * blocks, dtype=torch.int32, device=DEV).view(n_req, blocks)
+    n = n_req * q_len
+    ctx = SimpleNamespace(
+        cu_q=torch.from_numpy(np.arange(n_req + 1, dtype=np.int32) * q_len).to(DEV),
+        kv_len=torch.from_numpy(np.full(n_req, kv, dtype=np.int32)).to(DEV),
+        positions=torch.from_numpy(np.concatenate([np.arange(kv - q_len, kv, dtype=np.int32)] * n_req)).to(DEV),
+        tok_entry=torch.from_numpy(np.repeat(np.arange(n_req, dtype=np.int32), q_len)).to(DEV),
+        slots=torch.arange(n_req, dtype=torch.int32, device=DEV))
+    k_pool = torch.randn(n_req * blocks, G, ps, D, device=DEV).to(BF)
+    v_pool = torch.randn(n_req * blocks, G, ps, D, device=DEV).to(BF)
+    return ctx, table, k_pool, v_pool, n
+
+
+def scored_attention(a):
+    """The warp-level kernels for worked-on scores, heads stored at --head-dim: a prompt of --tokens, or with
+    --batch single tokens at --context (split along the keys, with the merge)."""
+    K = get_kernels([a.head_dim])
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    H, G, D = a.q_heads, a.kv_heads, a.head_dim
+    maps = 2 if a.weights == "two-maps" else 1
+    decode = a.batch > 0
+    n_req, q_len, kv = (a.batch, 1, a.context) if decode else (1, a.tokens, a.tokens)
+    ctx, table, k_pool, v_pool, n = _scored_setup(a, n_req, q_len, kv)
+    q = torch.randn(n, H * D, device=DEV).to(BF)
+    gate = torch.rand(n, H, device=DEV) if maps == 2 else None
+    mod = K.ScoreMod(softcap=a.softcap, chunk=a.block, sigmoid=a.weights == "sigmoid",
+                     head_bias=torch.randn(H, device=DEV) if a.weights == "sigmoid" else None, maps=maps, lam=0.4,
+                     head_norm=maps == 2, norm_scale=0.5, eps=1e-5, gate=gate, dv=D, compact=maps == 2)
+    o = torch.empty(n, H * D, device=DEV, dtype=BF)
+    scale = (D // maps) ** -0.5
+    seen = (min(a.block, kv) if a.block else kv)
+    if decode:
+        splits = a.splits or max(1, min(32, (2 * 148) // max(1, n_req * G)))
+        po = torch.empty(n_req * H * maps * splits, D, device=DEV)
+        pml = torch.empty(n_req * H * maps * splits, 2, device=DEV)
+        fn = lambda: K.scored_decode_attention(q, o, k_pool, v_pool, ctx.cu_q, ctx.kv_len, table, a.page_size, H, G, D, 0,
+                                               scale, splits, po, pml, mod, err)
+        t = _time(fn, a.warmup, a.reps)
+        _report(f"scored_decode_attn + merge ({a.weights}) batch {n_req} context {kv}", t,
+                n_req * min(kv, (kv - 1) % seen + 1 if a.block else kv) * G * D * 2 * 2, 0.0, {"splits": splits})
+    else:
+        tiles = -(-q_len // 64)
+        fn = lambda: K.scored_prefill_attention(q, o, k_pool, v_pool, ctx.cu_q, ctx.kv_len, table, a.page_size, tiles, H, G,
+                                                D, 0, scale, mod, err)
+        t = _time(fn, a.warmup, a.reps)
+        pairs = q_len * seen / 2 if a.block and a.block < q_len else q_len * q_len / 2
+        _report(f"scored_prefill_attn ({a.weights}) {q_len} tokens", t, 0, pairs * H * (2 * D + 2 * D * maps))
+    assert int(err.item()) == 0
+
+
+def scored_prep(a):
+    """What stands between the merged projection and the attention: convolutions, norms over the whole rows,
+    rotation, cache write."""
+    K = get_kernels([a.head_dim])
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    H, G, D = a.q_heads, a.kv_heads, a.head_dim
+    maps = 2 if a.two_maps else 1
+    dim = D // maps
+    decode = a.batch > 0
+    n_req, q_len, kv = (a.batch, 1, a.context) if decode else (1, a.tokens, a.tokens)
+    ctx, table, k_pool, v_pool, n = _scored_setup(a, n_req, q_len, kv)
+    cq, ck, cv = H * maps * dim, G * maps * dim, G * D
+    C = cq + ck + cv
+    cols = C + (H if maps == 2 else 0)
+    proj = torch.randn(n, cols, device=DEV).to(BF)
+    conv_w = torch.randn(C, a.taps, device=DEV) if a.taps else None
+    tails = torch.zeros(n_req, (a.taps - 1) * C, device=DEV) if a.taps > 1 else None
+    qw, kw = (torch.ones(cq, device=DEV), torch.ones(ck, device=DEV)) if a.norm else (None, None)
+    rot = dim // 2
+    cos, sin = torch.rand(kv, rot // 2, device=DEV), torch.rand(kv, rot // 2, device=DEV)
+    q = torch.empty(n, H * D, device=DEV, dtype=BF)
+    gate = torch.empty(n, H, device=DEV) if maps == 2 else None
+    fn = lambda: K.scored_prep(proj, cols, ctx, table, tails, conv_w, max(a.taps, 1), a.page_size, qw, kw, 1e-5, q, k_pool,
+                               v_pool, H, G, maps, dim, D, D // maps, cos, sin, rot, gate, C, err)
+    t = _time(fn, a.warmup, a.reps)
+    _report(f"scored_prep {n} tokens, {a.taps} taps, {maps} map(s)", t, n * C * 2 * 2, 0.0)
+    assert int(err.item()) == 0
+
+
 def hardware(a):
     """What one thread can issue and what a barrier across the SMs costs."""
     from ctypes import c_int, c_void_p
@@ -253,11 +342,25 @@ def main(argv=None) -> int:
     r = sub.add_parser("rmsnorm")
     r.add_argument("--rows", type=int, default=2048); r.add_argument("--hidden", type=int, default=2048)
     r.add_argument("--sets", type=int, default=1)
+    for name in ("scored-attention", "scored-prep"):
+        p = sub.add_parser(name)
+        p.add_argument("--q-heads", type=int, default=16); p.add_argument("--kv-heads", type=int, default=4)
+        p.add_argument("--head-dim", type=int, default=128); p.add_argument("--page-size", type=int, default=64)
+        p.add_argument("--batch", type=int, default=0, help="> 0: that many single tokens at --context")
+        p.add_argument("--context", type=int, default=8192); p.add_argument("--tokens", type=int, default=2048)
+        if name == "scored-attention":
+            p.add_argument("--weights", default="softmax", choices=["softmax", "sigmoid", "two-maps"])
+            p.add_argument("--softcap", type=float, default=0.0); p.add_argument("--block", type=int, default=0)
+            p.add_argument("--splits", type=int, default=0)
+        else:
+            p.add_argument("--taps", type=int, default=4); p.add_argument("--two-maps", action="store_true")
+            p.add_argument("--norm", action="store_true")
     a = ap.parse_args(argv)
     global GRAPH
     GRAPH = not a.no_graph
     {"gemm": gemm, "decode-attention": decode_attention, "prefill-attention": prefill_attention,
-     "rmsnorm": rmsnorm, "hardware": hardware}[a.what](a)
+     "rmsnorm": rmsnorm, "hardware": hardware, "scored-attention": scored_attention,
+     "scored-prep": scored_prep}[a.what](a)
     return 0
 
 
