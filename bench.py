@@ -1138,7 +1138,7 @@ def zudarax_kernel_table(zcfg, hcfg, pk, tokens, batch, context):
             C = cq + ck + cv
             cols = C + (H if maps == 2 else 0)
             proj = rnd(n, cols)
-            conv_w = rnd(C, taps, dt=f32) if taps else None
+            conv_w = rnd(taps, C, dt=f32) if taps else None
             tails = torch.zeros(n_req, (taps - 1) * C, device=dev) if taps > 1 else None
             qn, kn = (rnd(cq, dt=f32), rnd(ck, dt=f32)) if name == "attention" else (None, None)
             rot = m["rot"]["dims"]

@@ -8,7 +8,7 @@
 //    by the root of the mean square of what it is given.
 // 3. `scored_prep`: a token's row [q | k | v | gate] of the merged projection -> the query rows for the
 //    attention kernel, the token's key and value rows in the pages, sigmoid(gate) per head.  On the way:
-//    a causal convolution of a few taps over time on every channel (the inputs of the taps - 1 positions
+//    a causal convolution of a few taps over time on every channel (weights [taps][channels]; the inputs of the taps - 1 positions
 //    before the step come from the request's state slot), RMS norm of q and of k over their whole rows,
 //    rotation of the leading `rot_dims` elements of every head (element i with i + rot_dims / 2).  A head
 //    may hold several maps of `dim` elements (differential attention: two); each map turns like a head of
@@ -189,7 +189,7 @@ struct PrepArgs {
     int n_slots;
     const float* tails;             // [slots][taps - 1][C]: the convolutions' last inputs (taps > 1)
     long long slot_stride;
-    const float* conv_w;            // [C][taps], or null: no convolution
+    const float* conv_w;            // [taps][C] (a tap's weights of neighbouring channels side by side), or null
     int taps;
     const int* block_table;
     int max_blocks, num_pages, page_size;
@@ -273,8 +273,13 @@ scored_prep_kernel(GemmOut<T> proj, const PrepArgs a) {
                     if (VEC) { const float2 u = *(const float2*)p; u0 = u.x; u1 = u.y; }
                     else u0 = *p;
                 }
-                acc0 = fmaf(a.conv_w[(long long)c * taps + j], u0, acc0);
-                if (VEC) acc1 = fmaf(a.conv_w[(long long)(c + 1) * taps + j], u1, acc1);
+                if (VEC) {
+                    const float2 w = *(const float2*)(a.conv_w + (long long)j * C + c);
+                    acc0 = fmaf(w.x, u0, acc0);
+                    acc1 = fmaf(w.y, u1, acc1);
+                } else {
+                    acc0 = fmaf(a.conv_w[(long long)j * C + c], u0, acc0);
+                }
             }
             sm[c] = acc0;
             if (VEC) sm[c + 1] = acc1;
@@ -496,7 +501,7 @@ CRANE_API int crane_scored_prep(int dtype, const void* proj, const float* proj_p
         // pairs of channels where every width is even and a rotated half is too; the taps known at compile
         // time where they are few
         const bool vec = !(dim & 1) && !(dv & 1) && !(dpad & 1) && !(dk_store & 1) && !(dv_store & 1) && !(cols & 1) &&
-                         !(a.rot_dims & 3) && !(slot_stride & 1);
+                         !(a.rot_dims & 3) && !(slot_stride & 1) && !(C & 1);
         const int known = (conv_w != nullptr && taps >= 2 && taps <= 4) ? taps : 0;
         void (*kern)(GemmOut<T>, const PrepArgs) = nullptr;
         if (vec) kern = known == 2 ? scored_prep_kernel<T, 2, true> : known == 3 ? scored_prep_kernel<T, 3, true>

@@ -777,7 +777,7 @@ class Kernels:
                     k_pool, v_pool, H, G, maps, dim, dv, dpad, cos, sin, rot_dims, gate_out, gate_col, err) -> None:
         """Rows [q | k | v | gate] of a merged projection -> ``q_out`` [n, H, Dk], the token's rows in the
         pools [pages, G, page_size, Dk / Dv] (zero-filled where wider than the heads), ``gate_out`` float
-        [n, H] = sigmoid(gate).  ``tails`` float [slots, taps - 1, channels] with ``conv_w`` [channels, taps]:
+        [n, H] = sigmoid(gate).  ``tails`` float [slots, taps - 1, channels] with ``conv_w`` [taps, channels]:
         a causal convolution over time on every channel first, the slot's last inputs replaced afterwards.
         A head holds ``maps`` maps of ``dim`` elements, map i stored at i * ``dpad``."""
         whole, parts, n_parts, stride = _split(proj)

@@ -129,7 +129,8 @@ class ScoredAttention(Part):
             self.b_in = torch.cat(bias).contiguous()
         self.conv_w = None
         if self.taps >= 1:
-            self.conv_w = torch.cat([weights.pop(p + nm[n]) for n in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+            # [taps, channels]: a tap's weights of neighbouring channels side by side, as the kernel's lanes read them
+            self.conv_w = torch.cat([weights.pop(p + nm[n]) for n in ("q_conv", "k_conv", "v_conv")], dim=0).t().contiguous()
         norm = bool(a.get("qk_norm"))
         self.q_norm = weights[p + nm["q_norm"]] if norm else None
         self.k_norm = weights[p + nm["k_norm"]] if norm else None

@@ -265,7 +265,7 @@ def scored_prep(a):
     C = cq + ck + cv
     cols = C + (H if maps == 2 else 0)
     proj = torch.randn(n, cols, device=DEV).to(BF)
-    conv_w = torch.randn(C, a.taps, device=DEV) if a.taps else None
+    conv_w = torch.randn(a.taps, C, device=DEV) if a.taps else None
     tails = torch.zeros(n_req, (a.taps - 1) * C, device=DEV) if a.taps > 1 else None
     qw, kw = (torch.ones(cq, device=DEV), torch.ones(ck, device=DEV)) if a.norm else (None, None)
     rot = dim // 2

@@ -305,7 +305,7 @@ def test_scored_prep(K, dtype, H, G, maps, d, m, taps, norm, rot, dk_store, dpad
         table = _i32(full_table[[r for r, _, _, _ in ents]])
         q_out = torch.full((n + 1, H * dk_store), 5.0, dtype=dtype, device=DEV)
         gate = torch.full((n, H), 5.0, device=DEV) if gated else None
-        K.scored_prep(rows, cols, ctx, table, tails, None if conv_w is None else _dev(conv_w), max(taps, 1), ps,
+        K.scored_prep(rows, cols, ctx, table, tails, None if conv_w is None else _dev(conv_w.T.copy()), max(taps, 1), ps,
                       None if qw is None else _dev(qw), None if kw is None else _dev(kw), eps, q_out[:n], k_pool, v_pool,
                       H, G, maps, d, m, dpad, cos, sin, rot, gate, C, err)
         assert (q_out[n] == 5.0).all()
@@ -420,7 +420,7 @@ def test_scored_attention_with_planted_keys(K, dtype, splits, kind, H, G, d, m, 
         n = rows.shape[0]
         q_out = torch.empty(n, H * Dk, dtype=store, device=DEV)
         gate = torch.empty(n, H, device=DEV) if gated else None
-        K.scored_prep(rows, cols, ctx, table, tails, None if conv_w is None else _dev(conv_w), max(taps, 1), ps, None, None,
+        K.scored_prep(rows, cols, ctx, table, tails, None if conv_w is None else _dev(conv_w.T.copy()), max(taps, 1), ps, None, None,
                       eps, q_out, k_pool, v_pool, H, G, maps, d, m, dpad, cos, sin, rot, gate, C, err)
         if not splits:
             raw = torch.full((n, H * maps * m), 7.0, device=DEV) if finish else None
