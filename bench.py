@@ -1165,7 +1165,7 @@ def zudarax_kernel_table(zcfg, hcfg, pk, tokens, batch, context):
                     seen * H * (2 * D + 2 * D * maps), t_like, 0,
                     pairs * nq * 4 * d)
             else:
-                sp = max(1, min(32, (2 * 148) // max(1, n_req * G)))
+                sp = max(1, min(32, ((3 if maps == 2 else 2) * 148) // max(1, n_req * G)))
                 po = torch.empty(n_req * H * maps * sp, D, device=dev)
                 pml = torch.empty(n_req * H * maps * sp, 2, device=dev)
                 t_a = _median_ms(lambda: K.scored_decode_attention(q, o, k_pool, v_pool, cu_d, kv_d, table, ps, H, G, D, 0,

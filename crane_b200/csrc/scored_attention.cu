@@ -16,7 +16,7 @@
 // portions cut anywhere, whole prompts and single tokens are the same case.  `scored_decode_attn`: the
 // entries of exactly one token, split along the keys: one CTA per (slice of the keys, key/value head,
 // request), the query heads that share the key/value head in the rows of one MMA tile, each warp with its
-// own ring of three 32-key tiles; every slice leaves (max, sum, unnormalised sums) per head and map in
+// own ring of three 32-key tiles (two with two maps); every slice leaves (max, sum, unnormalised sums) per head and map in
 // scratch memory, and `scored_decode_merge` merges the slices and finishes the head.
 #include "attention_mma.cuh"
 
@@ -287,7 +287,10 @@ scored_prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* _
 }
 
 // ------------------------------------------------------------------ single tokens, split along the keys
-constexpr int TILE = 32, DWARPS = 2, NSTAGE = 3;
+constexpr int TILE = 32, DWARPS = 2;
+// tile stages per warp: with two maps a tile costs half as much again to work through, and two stages let a
+// third CTA move in on the SM
+template <int MAPS> constexpr int stages_of() { return MAPS == 2 ? 2 : 3; }
 
 // part_o [entry][head][map][slice][D], part_ml [entry][head][map][slice][2] (max in base 2, sum)
 template <int D, int MAPS>
@@ -301,6 +304,7 @@ scored_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, float* __restrict
     constexpr int RB = Tile<D>::ROW_BYTES;
     constexpr int TILE_BYTES = TILE * RB;
     constexpr int KS = D / 16, DN = D / 8, KSM = KS / MAPS;
+    constexpr int NSTAGE = stages_of<MAPS>();
     extern __shared__ __align__(16) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -583,7 +587,7 @@ int launch_scored_decode(const void* q, void* out, float* part_o, float* part_ml
                          const void* v_pool, const int* cu_q, const int* kv_len, const int* block_table,
                          int max_blocks, int num_pages, int page_size, int n_entries, int nq, int nkv, int window,
                          float scale, int n_splits, const ScoreArgs& sa, int* err, cudaStream_t st) {
-    constexpr int ring = DWARPS * NSTAGE * 2 * TILE * Tile<D>::ROW_BYTES;
+    constexpr int ring = DWARPS * stages_of<MAPS>() * 2 * TILE * Tile<D>::ROW_BYTES;
     constexpr int merge = DWARPS * MAPS * 16 * (D + 2) * (int)sizeof(float);
     constexpr int smem = ring > merge ? ring : merge;
     auto kern = scored_decode_attn_kernel<D, MAPS>;

@@ -223,7 +223,9 @@ def scored_attention_kernels(k, rt, ctx, q, o, cache, table, H, G, D, window, sc
     launches = 0
     if decode or singles:
         if decode:
-            splits = max(1, min(32, (2 * rt.num_sms) // max(1, ctx.n_entries * G)))
+            # enough slices for two CTAs an SM (three with two maps, whose CTAs hold two tile stages a warp)
+            per_sm = 3 if mod.maps == 2 else 2
+            splits = max(1, min(32, (per_sm * rt.num_sms) // max(1, ctx.n_entries * G)))
         else:
             splits = min(8, k.decode_splits(singles, G, rt.num_sms, max_splits))
         rows = rt.max_decode_rows * H * mod.maps * 32

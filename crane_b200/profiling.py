@@ -232,7 +232,7 @@ def scored_attention(a):
     scale = (D // maps) ** -0.5
     seen = (min(a.block, kv) if a.block else kv)
     if decode:
-        splits = a.splits or max(1, min(32, (2 * 148) // max(1, n_req * G)))
+        splits = a.splits or max(1, min(32, ((3 if maps == 2 else 2) * 148) // max(1, n_req * G)))
         po = torch.empty(n_req * H * maps * splits, D, device=DEV)
         pml = torch.empty(n_req * H * maps * splits, 2, device=DEV)
         fn = lambda: K.scored_decode_attention(q, o, k_pool, v_pool, ctx.cu_q, ctx.kv_len, table, a.page_size, H, G, D, 0,
