@@ -22,7 +22,7 @@ namespace {
 
 // ------------------------------------------------------ residual + norm in groups
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 add_group_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> a, int has_a, GemmOut<T> f, int has_f,
                          const float* __restrict__ w, const int* __restrict__ rows, T* __restrict__ out,
                          int width, int groups, float eps) {
@@ -32,6 +32,64 @@ add_group_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> a, int has_a, GemmOut
     pdl_wait();
     const int r = blockIdx.x;
     const long long base = (long long)(rows != nullptr ? rows[r] : r) * width;
+    const int gsize = width / groups;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    T* o = out + (long long)r * width;
+    // The row in 32 equal runs, where it splits so and a group is made of whole runs: a warp fetches, adds
+    // and squares a run at a time, the runs of a group are added up in order, and the warp that fetched a
+    // run writes it.  One barrier, all warps busy throughout, and the same sums whatever the number of warps.
+    constexpr int RUNS = 32;
+    const int seg = width / RUNS;
+    if (width % RUNS == 0 && seg > 0 && gsize % seg == 0) {
+        const bool pairs = (seg & 63) == 0;           // two neighbours a lane: loads and stores of pairs
+        for (int run = warp; run < RUNS; run += nwarps) {
+            const int c0 = run * seg;
+            float ss = 0.f;
+            if (pairs) {
+                for (int c = c0 + 2 * lane; c < c0 + seg; c += 64) {
+                    float2 v = ld2(x + base + c);
+                    if (has_a || has_f) {
+                        const float2 da = has_a ? a.load2(base + c) : make_float2(0.f, 0.f);
+                        const float2 df = has_f ? f.load2(base + c) : make_float2(0.f, 0.f);
+                        v.x += da.x + df.x;
+                        v.y += da.y + df.y;
+                        if (rows == nullptr) st2(x + base + c, v.x, v.y);
+                    }
+                    *(float2*)(row + c) = v;
+                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss));
+                }
+            } else {
+                for (int c = c0 + lane; c < c0 + seg; c += 32) {
+                    float v = x[base + c];
+                    if (has_a || has_f) {
+                        v += (has_a ? a.load(base + c) : 0.f) + (has_f ? f.load(base + c) : 0.f);
+                        if (rows == nullptr) x[base + c] = v;
+                    }
+                    row[c] = v;
+                    ss = fmaf(v, v, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) scratch[run] = ss;
+        }
+        __syncthreads();
+        const int per = gsize / seg;
+        for (int run = warp; run < RUNS; run += nwarps) {
+            const int c0 = run * seg, first = run / per * per;
+            float total = 0.f;
+            for (int i = 0; i < per; ++i) total += scratch[first + i];
+            const float rstd = rsqrtf(total / (float)gsize + eps);
+            if (pairs) {
+                for (int c = c0 + 2 * lane; c < c0 + seg; c += 64) {
+                    const float2 v = *(const float2*)(row + c), wv = ld2(w + c);
+                    st2(o + c, v.x * rstd * wv.x, v.y * rstd * wv.y);
+                }
+            } else {
+                for (int c = c0 + lane; c < c0 + seg; c += 32) o[c] = from_f32<T>(row[c] * rstd * w[c]);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = x[base + c];
         if (has_a || has_f) {
@@ -43,9 +101,6 @@ add_group_rmsnorm_kernel(float* __restrict__ x, GemmOut<T> a, int has_a, GemmOut
         row[c] = v;
     }
     __syncthreads();
-    const int gsize = width / groups;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    T* o = out + (long long)r * width;
     if (groups >= nwarps) {
         for (int g = warp; g < groups; g += nwarps) {
             const float* p = row + g * gsize;
@@ -431,7 +486,10 @@ CRANE_API int crane_add_group_rmsnorm(int dtype, float* x, const void* a, const 
                 configured = smem;
             }
         }
-        return crane_launch(kern, dim3(n_rows), dim3(256), smem, st, x, ga,
+        // few rows: more threads a row (what bounds them is the chain of loads a thread waits for), where the
+        // row goes in runs whose sums do not depend on the number of warps
+        const bool runs = width % 32 == 0 && (width / groups) % (width / 32) == 0;
+        return crane_launch(kern, dim3(n_rows), dim3(runs && n_rows <= 64 ? 1024 : 256), smem, st, x, ga,
                             (a != nullptr || a_parts != nullptr) ? 1 : 0, gf,
                             (f != nullptr || f_parts != nullptr) ? 1 : 0, w, rows, (T*)out, width, groups, eps);
     });
