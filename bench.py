@@ -1036,11 +1036,11 @@ def zudarax_config(like, layers):
     h, heads, kv = like["hidden_size"], like["num_attention_heads"], like["num_key_value_heads"]
     ff = like["intermediate_size"] * 3 // 2
     soft = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
-            "rot": {"dims": 64, "base": 10000.0}, "softcap": 30.0, "mask": {"size": 1024}}
+            "rot": {"dims": 64, "base": 10000.0}, "softcap": 50.0, "mask": {"size": 1024}}
     diff = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.5,
             "rot": {"dims": 32, "base": 10000.0}}
     sig = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
-           "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+           "rot": {"dims": 128, "base": 1000000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     kinds = (("attention", soft), ("attention_2", diff), ("attention_3", sig))
     ls = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]
     return {"architecture": "Zudarax", "vocab": like["vocab_size"], "width": h, "norm": {"eps": 1e-5, "groups": 8},

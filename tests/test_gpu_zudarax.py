@@ -353,7 +353,7 @@ def _plain_head(kind, q, k, v, pos, scale, cap, block, bias, lam, norm_scale, ep
 @pytest.mark.parametrize("kind, H, G, d, m, rot, ps, block, cap, taps", [
     ("soft", 4, 1, 64, 80, 32, 64, 100, 8.0, 3), ("soft", 6, 2, 16, 24, 8, 16, 24, 0.0, 0), ("soft", 2, 2, 100, 128, 100, 16, 0, 30.0, 2),
     ("sig", 3, 3, 24, 8, 0, 8, 0, 0.0, 2), ("sig", 8, 2, 128, 128, 64, 32, 0, 0.0, 4), ("sig", 5, 1, 48, 40, 16, 16, 50, 4.0, 0),
-    ("diff", 4, 2, 32, 64, 8, 16, 0, 0.0, 0), ("diff", 2, 2, 12, 40, 4, 16, 0, 0.0, 0), ("diff", 16, 2, 64, 128, 64, 32, 0, 0.0, 0),
+    ("diff", 6, 2, 32, 48, 16, 16, 0, 0.0, 0), ("diff", 2, 2, 12, 40, 4, 16, 0, 0.0, 0), ("diff", 16, 2, 64, 128, 64, 32, 0, 0.0, 0),
     ("diff", 3, 1, 16, 16, 16, 8, 20, 6.0, 3)])
 def test_scored_attention_with_planted_keys(K, dtype, splits, kind, H, G, d, m, rot, ps, block, cap, taps):
     """Preparation, cache write and attention over prompts and decoded tokens for every kind of weights.

@@ -67,7 +67,7 @@ ZB = {
 # values of 40; a head rotated wholly with YaRN; blocks of 33 positions over pages of 32; keys much wider
 # than values
 ZC = {
-    "architecture": "Zudarax", "vocab": 97, "width": 68, "norm": {"eps": 1e-6, "groups": 4},
+    "architecture": "Zudarax", "vocab": 97, "width": 68, "norm": {"eps": 2e-6, "groups": 4},
     "layers": [
         _layer("attention_2", _diff(2, 1, 12, 40, 0.3, 0.5, rot=_rot(4, 50.0)), 24),
         _layer("attention_3", _soft(3, 3, 20, 12, 0.2, conv=4, rot=_rot(20, 300.0, (1.5, 40, 4.0, 0.5))), 100),
