@@ -501,7 +501,9 @@ CRANE_API int crane_poly_norm(int dtype, const void* up, const float* up_parts, 
     const size_t smem = (size_t)F * sizeof(float);
     const bool cached = smem <= 96 * 1024;
     // few rows: more threads a row (what bounds them is the chain of loads a thread waits for)
-    const int threads = n_rows <= 64 ? 1024 : 256;
+    // (bfloat16 only: in true 32-bit the sums keep one order whatever the step's size, so that a position's
+    // logits do not depend on how its request was cut, to the bit)
+    const int threads = (dtype == 1 && n_rows <= 64) ? 1024 : 256;
     if (dtype == 1 && up != nullptr && n_rows > 64 && F % 8 == 0 && F <= 16384 && ((uintptr_t)up & 15) == 0 &&
         ((uintptr_t)out & 15) == 0) {
         const __nv_bfloat16* u = (const __nv_bfloat16*)up;
@@ -571,7 +573,8 @@ CRANE_API int crane_scored_prep(int dtype, const void* proj, const float* proj_p
                 return (int)cudaGetLastError();
         }
         // few tokens: more threads a token (what bounds them is the chain of loads a thread waits for)
-        int rc = crane_launch(kern, dim3(n_tokens), dim3(n_tokens <= 64 ? 1024 : 256), smem, st, g, a);
+        // (bfloat16 only: in true 32-bit the sums keep one order whatever the step's size)
+        int rc = crane_launch(kern, dim3(n_tokens), dim3((dtype == 1 && n_tokens <= 64) ? 1024 : 256), smem, st, g, a);
         if (rc != 0 || taps <= 1 || tails == nullptr) return rc;
         return crane_launch(conv_tail_update_kernel<T>, dim3((C + 127) / 128, n_entries), dim3(128), 0, st, g, cols,
                             cu_q, kv_len, slots, n_slots, tails, slot_stride, taps, C);
